@@ -1,0 +1,96 @@
+// Launch interface between the host runtime and the CUDA translation units.  Plain
+// pointers only, so the kernel files never include torch headers.
+//
+// One exchange is four launches, two per role:
+//   attention: launch_dispatch  ...  launch_collect
+//   FFN:       launch_receive   ...  launch_reply
+// The reference needs the same four entry points on *every* rank plus two global GPU
+// barriers around each transport kernel (deep_ep/include/deep_ep/impls/dispatch.cuh,
+// combine.cuh); here ranks only ever wait on point-to-point epoch flags.
+#pragma once
+#include <cuda_runtime.h>
+
+#include "layout.h"
+
+namespace afdep {
+
+struct RankCtx {
+    Geometry g;
+    int rank;        // global rank, FFN ranks first
+    int role_rank;   // index among the ranks of the same role
+    char* peer[kMaxRanks];   // heap base of every rank as mapped into this process
+    Status* status;  // device pointer to mapped pinned host memory
+    int* poison;     // device word
+    long long budget;   // clock64 ticks a wait may spin
+    int bounds_check;   // verify computed rows/slots before use
+};
+
+// Device-local scratch of an attention rank (not visible to peers).
+struct AttnWs {
+    unsigned* epoch;    // [0] dispatch, [1] collect: exchanges completed so far
+    unsigned* ticket;   // [0] dispatch, [1] collect: CTAs that reached the end of the launch
+    unsigned long long* agg;   // [max_ctas][ffn + num_experts]: (epoch << 32 | count)
+    int* route_e;       // [capacity][top_k] expert or -1
+    int* route_pos;     // [capacity][top_k] rank of the choice within (source, expert)
+    int* tok_slot;      // [capacity][ffn] record slot on that FFN rank or -1
+};
+
+// Device-local scratch of an FFN rank.
+struct FfnWs {
+    unsigned* epoch;    // [0] receive, [1] reply, [2] host-count sequence
+    unsigned* ticket;   // [0] receive, [1] reply
+    int* row_base;      // [attn][experts_local] first row of (source, expert)
+    int* rec_prefix;    // [attn + 1] prefix sum of records per source
+    int* ends;          // [experts_local] copy of the last receive's prefix sums
+    int* host_counts;   // mapped pinned host memory: [experts_local] aligned counts, then seq
+};
+
+struct DispatchArgs {
+    const void* x;          // [T][hidden] bf16 or e4m3, contiguous
+    const float* x_scale;   // FP8 only: element (t, g) at x_scale[t * ss0 + g * ss1]
+    long long ss0, ss1;
+    const long long* ids;   // [T][top_k] int64
+    const float* weights;   // [T][top_k]
+    int T;
+};
+
+struct ReceiveArgs {
+    void* recv_x;           // [rows_cap][hidden]
+    float* recv_scale;      // FP8 only: element (row, g) at recv_scale[row * rs0 + g * rs1]
+    long long rs0, rs1;
+    float* recv_w;          // [rows_cap]
+    int* recv_src;          // [rows_cap][2]: source attention rank, source token
+    int* psum;              // [experts_local] end row of every expert segment
+    int rows_cap;
+    int layout_ready;       // 1: launch_ffn_layout already ran for this exchange
+    int write_host_counts;  // layout kernel only
+};
+
+struct LaunchShape {
+    int ctas;
+    int warps;
+    int smem_bytes;
+};
+
+// Pick warps/smem for a kernel given the CTA budget and the device's opt-in shared memory.
+LaunchShape dispatch_shape(const Geometry& g, int tokens, int num_sms, int max_smem);
+LaunchShape receive_shape(const Geometry& g, int num_sms, int max_smem);
+LaunchShape reply_shape(const Geometry& g, int num_sms, int max_smem);
+LaunchShape collect_shape(const Geometry& g, int tokens, int num_sms, int max_smem);
+int max_dispatch_ctas();   // rows of AttnWs::agg
+
+cudaError_t launch_dispatch(const RankCtx& c, const AttnWs& ws, const DispatchArgs& a, LaunchShape s,
+                            cudaStream_t stream);
+cudaError_t launch_collect(const RankCtx& c, const AttnWs& ws, void* out, int T, LaunchShape s,
+                           cudaStream_t stream);
+cudaError_t launch_ffn_layout(const RankCtx& c, const FfnWs& ws, const ReceiveArgs& r, cudaStream_t stream);
+cudaError_t launch_receive(const RankCtx& c, const FfnWs& ws, const ReceiveArgs& r, LaunchShape s,
+                           cudaStream_t stream);
+cudaError_t launch_reply(const RankCtx& c, const FfnWs& ws, const void* rows, int rows_cap, LaunchShape s,
+                         cudaStream_t stream);
+cudaError_t launch_barrier(const RankCtx& c, unsigned* epoch_word, cudaStream_t stream);
+
+// One-time per process: raise the dynamic shared memory limit of every kernel.
+cudaError_t configure_kernels(int max_smem);
+
+}  // namespace afdep

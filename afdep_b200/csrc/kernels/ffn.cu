@@ -1,0 +1,434 @@
+// FFN-side kernels: receive (wait, place, expand) and reply (pre-reduce, publish).
+//
+// receive — every CTA first derives the exchange's row layout from the count vectors the
+// sources pushed (bounded wait on one epoch flag per source): per-expert totals, aligned
+// segment starts, `ends[]`, and the first row of every (source, expert) pair.  Then warps
+// take wire records (source, slot) one at a time: poll the record's 4-byte arrival flag,
+// pull the record into shared memory with one bulk copy, and write the payload once per
+// local expert the token chose, at row_base[source][expert] + pos — a placement the sender
+// already made deterministic, so no atomics and no second pass.  Expansion traffic stays in
+// local HBM; NVLink carried the row only once per (token, FFN rank).
+//
+// reply — one warp per record again: sum the token's local expert rows (fp32 accumulate in
+// top-k order, one rounding to BF16; a single row is copied bit-exactly) into the reply slot
+// the attention rank will pull from, then release that rank's flag for the slot.
+//
+// Together they replace the reference's dispatch_copy_epilogue_impl, the sender half of
+// combine_impl and the host's CPU polling loop (deep_ep/include/deep_ep/impls/
+// dispatch_copy_epilogue.cuh, combine.cuh; csrc/elastic/buffer.hpp:994-1041).
+#include <cuda_bf16.h>
+
+#include "afdep/kernels.h"
+#include "afdep/status.cuh"
+
+namespace afdep {
+
+namespace {
+
+constexpr int kNB = 2;
+constexpr int kBarBytes = 512;
+constexpr int kMaxWarps = 16;
+
+struct LayoutSmem {
+    int row_base[kMaxRanks * kMaxExpertsLocal];   // [attn][experts_local]
+    int tot[kMaxExpertsLocal];
+    int start[kMaxExpertsLocal];
+    int rec_prefix[kMaxRanks + 1];
+    int dead;
+};
+
+__device__ __forceinline__ int align_up_dev(int v, int a) { return (v + a - 1) / a * a; }
+
+// Runs in every CTA of the receive kernel (and alone in the layout kernel).  Returns false,
+// uniformly for the CTA, if a source's counts never arrived.
+__device__ bool compute_layout(const RankCtx& c, const WaitCtx& wc, unsigned ep, LayoutSmem& L) {
+    const Geometry& g = c.g;
+    const int tid = threadIdx.x;
+    const int A = g.attn, EL = g.experts_local, cs = cnt_stride(g);
+    unsigned char* heap = reinterpret_cast<unsigned char*>(c.peer[c.rank]);
+    const uint32_t* cnt_flag = reinterpret_cast<const uint32_t*>(heap + g.f_cnt_flag);
+    const int* cnt = reinterpret_cast<const int*>(heap + g.f_cnt);
+    if (tid == 0) L.dead = 0;
+    __syncthreads();
+    if (tid < A) {
+        uint32_t seen = 0;
+        const bool ok = spin_until(wc, [&] {
+            seen = ptx::ld_acquire_sys(cnt_flag + tid * 32);
+            return seen == ep;
+        });
+        if (!ok) {
+            report(wc, kTimeoutCounts, g.ffn + tid, ep, ep, seen);
+            poison(wc);
+            L.dead = 1;
+        }
+    }
+    __syncthreads();
+    if (L.dead) return false;
+
+    for (int el = tid; el < EL; el += blockDim.x) {
+        int t = 0;
+        for (int a = 0; a < A; ++a) t += __ldcg(cnt + a * cs + el);
+        L.tot[el] = t;
+    }
+    __syncthreads();
+    if (tid < 32) {
+        // exclusive scan of the aligned totals, a contiguous run of experts per lane
+        const int per = (EL + 31) / 32;
+        const int lo = min(EL, tid * per), hi = min(EL, lo + per);
+        int sum = 0;
+        for (int el = lo; el < hi; ++el) sum += align_up_dev(L.tot[el], g.alignment);
+        int inc = sum;
+        for (int d = 1; d < 32; d <<= 1) {
+            const int v = __shfl_up_sync(ptx::kFullMask, inc, d);
+            if (tid >= d) inc += v;
+        }
+        int run = inc - sum;
+        for (int el = lo; el < hi; ++el) {
+            L.start[el] = run;
+            run += align_up_dev(L.tot[el], g.alignment);
+        }
+    }
+    if (tid == 32 || (blockDim.x <= 32 && tid == 0)) {
+        int run = 0;
+        for (int a = 0; a < A; ++a) {
+            L.rec_prefix[a] = run;
+            run += __ldcg(cnt + a * cs + EL);
+        }
+        L.rec_prefix[A] = run;
+    }
+    __syncthreads();
+    for (int el = tid; el < EL; el += blockDim.x) {
+        int run = L.start[el];
+        for (int a = 0; a < A; ++a) {
+            L.row_base[a * EL + el] = run;
+            run += __ldcg(cnt + a * cs + el);
+        }
+    }
+    __syncthreads();
+    return true;
+}
+
+__device__ void publish_layout(const RankCtx& c, const FfnWs& ws, const ReceiveArgs& r, const LayoutSmem& L) {
+    const Geometry& g = c.g;
+    const int A = g.attn, EL = g.experts_local;
+    for (int el = threadIdx.x; el < EL; el += blockDim.x) {
+        const int end = L.start[el] + L.tot[el];
+        if (r.psum) r.psum[el] = end;
+        ws.ends[el] = end;
+    }
+    for (int i = threadIdx.x; i < A * EL; i += blockDim.x) ws.row_base[i] = L.row_base[i];
+    for (int i = threadIdx.x; i <= A; i += blockDim.x) ws.rec_prefix[i] = L.rec_prefix[i];
+}
+
+__device__ void load_layout(const RankCtx& c, const FfnWs& ws, LayoutSmem& L) {
+    const Geometry& g = c.g;
+    const int A = g.attn, EL = g.experts_local;
+    for (int i = threadIdx.x; i < A * EL; i += blockDim.x) L.row_base[i] = ws.row_base[i];
+    for (int i = threadIdx.x; i <= A; i += blockDim.x) L.rec_prefix[i] = ws.rec_prefix[i];
+    if (threadIdx.x == 0) L.dead = 0;
+    __syncthreads();
+}
+
+// Stand-alone layout pass, used when the host wants exact counts before it allocates the
+// receive tensors.  Writes aligned per-expert counts and a sequence number to mapped host
+// memory; the receive kernel that follows is launched with layout_ready = 1.
+__global__ void __launch_bounds__(256, 1) ffn_layout_kernel(const RankCtx c, const FfnWs ws, const ReceiveArgs r) {
+    __shared__ LayoutSmem L;
+    const Geometry& g = c.g;
+    const unsigned ep = ptx::ld_acquire_gpu(&ws.epoch[0]) + 1u;
+    const WaitCtx wc{c.status, c.poison, c.budget, c.rank, /*kernel=*/2};
+    const bool ok = compute_layout(c, wc, ep, L);
+    if (ok) publish_layout(c, ws, r, L);
+    __syncthreads();
+    if (r.write_host_counts) {
+        volatile int* hc = ws.host_counts;
+        for (int el = threadIdx.x; el < g.experts_local; el += blockDim.x)
+            hc[el] = ok ? align_up_dev(L.tot[el], g.alignment) : 0;
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const unsigned seq = ws.epoch[2] + 1u;
+            ws.epoch[2] = seq;
+            hc[g.experts_local] = ok ? (int)seq : -(int)seq;
+            __threadfence_system();
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kMaxWarps * 32, 1)
+receive_kernel(const RankCtx c, const FfnWs ws, const ReceiveArgs r) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ LayoutSmem L;
+    const Geometry& g = c.g;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, NW = blockDim.x >> 5;
+    const int G = gridDim.x, cta = blockIdx.x;
+    const int A = g.attn, K = g.top_k, EL = g.experts_local, C = g.capacity;
+    const int fi = c.role_rank;
+    const unsigned ep = ptx::ld_acquire_gpu(&ws.epoch[0]) + 1u;
+    const WaitCtx wc{c.status, c.poison, c.budget, c.rank, /*kernel=*/3};
+    unsigned char* heap = reinterpret_cast<unsigned char*>(c.peer[c.rank]);
+
+    bool ok = true;
+    if (r.layout_ready) {
+        load_layout(c, ws, L);
+    } else {
+        ok = compute_layout(c, wc, ep, L);
+        if (ok && cta == 0) publish_layout(c, ws, r, L);
+    }
+
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
+    unsigned char* bufs = smem + kBarBytes + (size_t)warp * kNB * g.rec_bytes;
+    if (lane == 0) {
+        for (int b = 0; b < kNB; ++b) ptx::mbar_init(&bars[warp * kNB + b], 1);
+        ptx::fence_mbar_init();
+    }
+    __syncwarp();
+
+    const uint32_t* slot_flag = reinterpret_cast<const uint32_t*>(heap + g.f_slot_flag);
+    const unsigned char* stage = heap + g.f_stage;
+    const int used = g.meta_off + g.meta_bytes;     // bytes of a record that carry data
+    const int total = ok ? L.rec_prefix[A] : 0;
+    const int sg = g.fp8 ? g.scale_groups : 0;
+    unsigned char* rx = static_cast<unsigned char*>(r.recv_x);
+    int it = 0;
+    for (int item = cta * NW + warp; item < total; item += G * NW) {
+        int a = 0;
+        while (a + 1 < A && item >= L.rec_prefix[a + 1]) ++a;
+        const int slot = item - L.rec_prefix[a];
+        bool arrived = true;
+        if (lane == 0) {
+            uint32_t seen = 0;
+            arrived = spin_until(wc, [&] {
+                seen = ptx::ld_acquire_sys(slot_flag + (size_t)a * C + slot);
+                return seen == ep;
+            });
+            if (!arrived) {
+                report(wc, kTimeoutRecord, g.ffn + a, ep, ep, seen, slot, total);
+                poison(wc);
+            }
+        }
+        arrived = __shfl_sync(ptx::kFullMask, arrived, 0);
+        if (!arrived) break;
+        const int b = it % kNB;
+        const unsigned parity = (it / kNB) & 1u;
+        unsigned char* buf = bufs + (size_t)b * g.rec_bytes;
+        uint64_t* bar = &bars[warp * kNB + b];
+        if (lane == 0) {
+            if (it >= kNB) ptx::bulk_wait_read<kNB - 1>();
+            ptx::fence_proxy_async_global();
+            ptx::mbar_expect_tx(bar, used);
+            ptx::bulk_load(buf, stage + ((size_t)a * C + slot) * g.rec_bytes, used, bar);
+        }
+        bool landed = spin_until(wc, [&] { return ptx::mbar_try_wait(bar, parity); });
+        landed = __all_sync(ptx::kFullMask, landed);
+        if (!landed) break;
+
+        const int* meta = reinterpret_cast<const int*>(buf + g.meta_off);
+        int row = -1;
+        float w = 0.f;
+        if (lane < K) {
+            const int e = meta[lane];
+            const int el = e - fi * EL;
+            if (e >= 0 && el >= 0 && el < EL) {
+                row = L.row_base[a * EL + el] + meta[K + lane];
+                w = reinterpret_cast<const float*>(meta)[2 * K + lane];
+                if (row < 0 || row >= r.rows_cap) {
+                    report(wc, kBadIndex, g.ffn + a, ep, r.rows_cap, row, slot, 3);
+                    row = -1;
+                }
+            }
+        }
+        const int src_token = meta[3 * K];
+        const unsigned hits = __ballot_sync(ptx::kFullMask, row >= 0);
+        for (unsigned m = hits; m; m &= m - 1) {
+            const int k = __ffs(m) - 1;
+            const int rk = __shfl_sync(ptx::kFullMask, row, k);
+            if (lane == 0) ptx::bulk_store(rx + (size_t)rk * g.payload_bytes, buf, g.payload_bytes);
+            const float* sc = reinterpret_cast<const float*>(buf + g.payload_bytes);
+            for (int gi = lane; gi < sg; gi += 32) r.recv_scale[(size_t)rk * r.rs0 + (size_t)gi * r.rs1] = sc[gi];
+        }
+        if (lane == 0) ptx::bulk_commit();
+        if (row >= 0) {
+            r.recv_w[row] = w;
+            r.recv_src[2 * (size_t)row] = a;
+            r.recv_src[2 * (size_t)row + 1] = src_token;
+        }
+        __syncwarp();
+        ++it;
+    }
+    if (lane == 0) ptx::bulk_wait<0>();
+
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        if (atomicAdd(&ws.ticket[0], 1u) == (unsigned)(G - 1)) {
+            ws.ticket[0] = 0;
+            ws.epoch[0] = ep;
+            __threadfence();
+        }
+    }
+}
+
+__device__ __forceinline__ void acc_bf16x8(float* acc, const uint4& v) {
+    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(p[i]);
+        acc[2 * i] += f.x;
+        acc[2 * i + 1] += f.y;
+    }
+}
+__device__ __forceinline__ uint4 pack_bf16x8(const float* acc) {
+    uint4 v;
+    __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) p[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+    return v;
+}
+
+__global__ void __launch_bounds__(kMaxWarps * 32, 1)
+reply_kernel(const RankCtx c, const FfnWs ws, const unsigned char* __restrict__ rows, int rows_cap) {
+    __shared__ LayoutSmem L;
+    __shared__ int s_rows[kMaxWarps][kMaxTopK];
+    const Geometry& g = c.g;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, NW = blockDim.x >> 5;
+    const int G = gridDim.x, cta = blockIdx.x;
+    const int A = g.attn, K = g.top_k, EL = g.experts_local, C = g.capacity;
+    const int fi = c.role_rank;
+    const unsigned ep = ptx::ld_acquire_gpu(&ws.epoch[1]) + 1u;
+    const WaitCtx wc{c.status, c.poison, c.budget, c.rank, /*kernel=*/4};
+    unsigned char* heap = reinterpret_cast<unsigned char*>(c.peer[c.rank]);
+    load_layout(c, ws, L);
+    const bool dead = poisoned(wc);   // an abandoned receive leaves no layout to reply to
+
+    const unsigned char* stage = heap + g.f_stage;
+    unsigned char* reply = heap + g.f_reply;
+    const int total = dead ? 0 : L.rec_prefix[A];
+    const int nvec = g.hidden / 8;    // 16-byte vectors per row
+    for (int item = cta * NW + warp; item < total; item += G * NW) {
+        int a = 0;
+        while (a + 1 < A && item >= L.rec_prefix[a + 1]) ++a;
+        const int slot = item - L.rec_prefix[a];
+        const int* meta = reinterpret_cast<const int*>(stage + ((size_t)a * C + slot) * g.rec_bytes + g.meta_off);
+        int row = -1;
+        if (lane < K) {
+            const int e = __ldcg(meta + lane);
+            const int el = e - fi * EL;
+            if (e >= 0 && el >= 0 && el < EL) {
+                row = L.row_base[a * EL + el] + __ldcg(meta + K + lane);
+                if (row < 0 || row >= rows_cap) row = -1;
+            }
+        }
+        const unsigned hits = __ballot_sync(ptx::kFullMask, row >= 0);
+        const int nh = __popc(hits);
+        if (row >= 0) s_rows[warp][__popc(hits & ptx::lanemask_lt())] = row;
+        __syncwarp();
+        unsigned char* out = reply + ((size_t)a * C + slot) * g.row_bytes;
+        if (nh == 1) {
+            const unsigned char* src = rows + (size_t)s_rows[warp][0] * g.row_bytes;
+            for (int v = lane; v < nvec; v += 32 * 4) {
+                uint4 x[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (v + u * 32 < nvec) x[u] = *reinterpret_cast<const uint4*>(src + (size_t)(v + u * 32) * 16);
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (v + u * 32 < nvec) *reinterpret_cast<uint4*>(out + (size_t)(v + u * 32) * 16) = x[u];
+            }
+        } else {
+            for (int v = lane; v < nvec; v += 32 * 2) {
+                float acc[2][8];
+#pragma unroll
+                for (int u = 0; u < 2; ++u)
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) acc[u][i] = 0.f;
+                for (int h = 0; h < nh; ++h) {
+                    const unsigned char* src = rows + (size_t)s_rows[warp][h] * g.row_bytes;
+                    uint4 x[2];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u)
+                        if (v + u * 32 < nvec) x[u] = *reinterpret_cast<const uint4*>(src + (size_t)(v + u * 32) * 16);
+#pragma unroll
+                    for (int u = 0; u < 2; ++u)
+                        if (v + u * 32 < nvec) acc_bf16x8(acc[u], x[u]);
+                }
+#pragma unroll
+                for (int u = 0; u < 2; ++u)
+                    if (v + u * 32 < nvec)
+                        *reinterpret_cast<uint4*>(out + (size_t)(v + u * 32) * 16) = pack_bf16x8(acc[u]);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) {
+            ptx::fence_acq_rel_sys();
+            uint32_t* flag = reinterpret_cast<uint32_t*>(c.peer[g.ffn + a] + g.a_reply_flag) + (size_t)fi * C + slot;
+            ptx::st_relaxed_sys(flag, ep);
+        }
+    }
+
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence();
+        if (atomicAdd(&ws.ticket[1], 1u) == (unsigned)(G - 1)) {
+            ws.ticket[1] = 0;
+            ws.epoch[1] = ep;
+            __threadfence();
+        }
+    }
+}
+
+}  // namespace
+
+// Static shared memory of the receive kernel, measured once by configure_ffn.
+static int g_receive_static = (int)sizeof(LayoutSmem) + 1024;
+
+LaunchShape receive_shape(const Geometry& g, int num_sms, int max_smem) {
+    LaunchShape s{};
+    int avail = max_smem - kBarBytes - g_receive_static;
+    int warps = avail / (kNB * g.rec_bytes);
+    if (warps > kMaxWarps) warps = kMaxWarps;
+    if (warps < 1) warps = 1;
+    s.ctas = num_sms;
+    s.warps = warps;
+    s.smem_bytes = kBarBytes + warps * kNB * g.rec_bytes;
+    return s;
+}
+
+LaunchShape reply_shape(const Geometry& g, int num_sms, int max_smem) {
+    (void)g;
+    (void)max_smem;
+    LaunchShape s{};
+    s.ctas = num_sms;
+    s.warps = kMaxWarps;
+    s.smem_bytes = 0;
+    return s;
+}
+
+cudaError_t launch_ffn_layout(const RankCtx& c, const FfnWs& ws, const ReceiveArgs& r, cudaStream_t stream) {
+    ffn_layout_kernel<<<1, 256, 0, stream>>>(c, ws, r);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_receive(const RankCtx& c, const FfnWs& ws, const ReceiveArgs& r, LaunchShape s,
+                           cudaStream_t stream) {
+    receive_kernel<<<s.ctas, s.warps * 32, s.smem_bytes, stream>>>(c, ws, r);
+    return cudaGetLastError();
+}
+
+cudaError_t launch_reply(const RankCtx& c, const FfnWs& ws, const void* rows, int rows_cap, LaunchShape s,
+                         cudaStream_t stream) {
+    reply_kernel<<<s.ctas, s.warps * 32, s.smem_bytes, stream>>>(c, ws, static_cast<const unsigned char*>(rows),
+                                                                rows_cap);
+    return cudaGetLastError();
+}
+
+cudaError_t configure_ffn(int max_smem) {
+    cudaFuncAttributes attr;
+    cudaError_t e = cudaFuncGetAttributes(&attr, receive_kernel);
+    if (e != cudaSuccess) return e;
+    g_receive_static = (int)attr.sharedSizeBytes;
+    return cudaFuncSetAttribute(receive_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                max_smem - g_receive_static);
+}
+
+}  // namespace afdep

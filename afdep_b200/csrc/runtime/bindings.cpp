@@ -1,0 +1,390 @@
+// Host runtime of one rank's Buffer and its Python bindings.
+//
+// NativeBuffer owns the symmetric heap, the device-local scratch of the rank's role, the
+// mapped-host status block, and launches the exchange kernels on the caller's current
+// CUDA stream.  Nothing here synchronises with the device except construction, destroy()
+// and the optional exact-count path of worker_receive; epochs live in device memory, so a
+// captured CUDA graph replays an exchange without host involvement.
+//
+// Counterpart of the reference's ElasticBuffer host class (csrc/elastic/buffer.hpp:19-1347)
+// and pybind module (csrc/python_api.cpp), without NCCL, JIT or a comm-stream detour.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <pybind11/stl.h>
+#include <torch/extension.h>
+
+#include <chrono>
+#include <memory>
+#include <thread>
+
+#include "afdep/kernels.h"
+#include "driver.hpp"
+#include "heap.hpp"
+
+namespace py = pybind11;
+
+namespace afdep {
+
+namespace {
+
+const char* code_name(int code) {
+    switch (code) {
+        case kOk: return "ok";
+        case kTimeoutCounts: return "timeout waiting for a source's counts";
+        case kTimeoutRecord: return "timeout waiting for a record";
+        case kTimeoutReply: return "timeout waiting for a reply row";
+        case kTimeoutLookback: return "timeout in the dispatch look-back";
+        case kTimeoutBarrier: return "timeout in barrier";
+        case kTimeoutAux: return "timeout in an auxiliary primitive";
+        case kBadRoute: return "illegal route";
+        case kBadIndex: return "computed index out of bounds";
+        default: return "unknown";
+    }
+}
+
+SymmetricHeap::Mode parse_mode(const std::string& m) {
+    if (m == "vmm") return SymmetricHeap::Mode::kVmmFd;
+    if (m == "ipc") return SymmetricHeap::Mode::kCudaIpc;
+    if (m == "plain") return SymmetricHeap::Mode::kPlain;
+    throw std::invalid_argument("heap mode must be 'vmm', 'ipc' or 'plain'");
+}
+
+}  // namespace
+
+class NativeBuffer {
+public:
+    NativeBuffer(int rank, int ffn, int attn, int hidden, int top_k, int num_experts, int capacity, bool fp8,
+                 int alignment, int num_sms, int collect_sms, int ffn_sms, double gpu_timeout_s,
+                 int64_t aux_bytes, const std::string& heap_mode, bool bounds_check)
+        : rank_(rank), num_sms_(num_sms), collect_sms_(collect_sms), ffn_sms_(ffn_sms) {
+        TORCH_CHECK(ffn + attn <= kMaxRanks, "the native transport supports at most ", kMaxRanks, " ranks");
+        TORCH_CHECK(num_experts <= kMaxExperts && num_experts / ffn <= kMaxExpertsLocal, "too many experts");
+        TORCH_CHECK(top_k <= kMaxTopK, "top_k too large");
+        rt_check(cudaGetDevice(&device_), "cudaGetDevice");
+        geo_ = make_geometry(ffn, attn, hidden, top_k, num_experts, capacity, fp8 ? 1 : 0, alignment, (size_t)aux_bytes);
+        is_ffn_ = rank < ffn;
+        role_rank_ = is_ffn_ ? rank : rank - ffn;
+        const size_t bytes = is_ffn_ ? geo_.f_bytes : geo_.a_bytes;
+        heap_ = std::make_unique<SymmetricHeap>(device_, bytes, parse_mode(heap_mode));
+        rt_check(cudaMemset(heap_->local(), 0, bytes), "cudaMemset(heap)");
+
+        int sms = 0, smem = 0, khz = 0;
+        rt_check(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device_), "device attribute");
+        rt_check(cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, device_), "device attribute");
+        rt_check(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, device_), "device attribute");
+        device_sms_ = sms;
+        max_smem_ = smem;
+        if (num_sms_ <= 0 || num_sms_ > sms) num_sms_ = sms;
+        if (collect_sms_ <= 0 || collect_sms_ > sms) collect_sms_ = sms;
+        if (ffn_sms_ <= 0 || ffn_sms_ > sms) ffn_sms_ = sms;
+        rt_check(configure_kernels(max_smem_), "cudaFuncSetAttribute");
+
+        // status block and host-count mailbox in mapped pinned memory
+        rt_check(cudaHostAlloc(&host_block_, kHostBlockBytes, cudaHostAllocMapped), "cudaHostAlloc");
+        std::memset(host_block_, 0, kHostBlockBytes);
+        void* dev_view = nullptr;
+        rt_check(cudaHostGetDevicePointer(&dev_view, host_block_, 0), "cudaHostGetDevicePointer");
+
+        auto i32 = torch::TensorOptions().dtype(torch::kInt32).device(torch::kCUDA, device_);
+        flags_ = torch::zeros({64}, i32);   // poison words, epochs, tickets
+        int* fl = flags_.data_ptr<int>();
+        ctx_.g = geo_;
+        ctx_.rank = rank;
+        ctx_.role_rank = role_rank_;
+        for (int i = 0; i < kMaxRanks; ++i) ctx_.peer[i] = nullptr;
+        ctx_.peer[rank] = static_cast<char*>(heap_->local());
+        ctx_.status = static_cast<Status*>(dev_view);
+        ctx_.poison = fl;                       // words 0..3
+        ctx_.budget = (long long)(gpu_timeout_s * 1000.0 * (double)khz);
+        ctx_.bounds_check = bounds_check ? 1 : 0;
+        barrier_epoch_ = reinterpret_cast<unsigned*>(fl + 8);
+        if (is_ffn_) {
+            fws_.epoch = reinterpret_cast<unsigned*>(fl + 16);    // 3 words
+            fws_.ticket = reinterpret_cast<unsigned*>(fl + 24);   // 2 words
+            scratch_ = torch::zeros({(int64_t)attn * geo_.experts_local + attn + 1 + geo_.experts_local + 8}, i32);
+            int* s = scratch_.data_ptr<int>();
+            fws_.row_base = s;
+            fws_.rec_prefix = s + (size_t)attn * geo_.experts_local;
+            fws_.ends = fws_.rec_prefix + attn + 1;
+            fws_.host_counts = reinterpret_cast<int*>(static_cast<char*>(dev_view) + kHostCountsOff);
+        } else {
+            aws_.epoch = reinterpret_cast<unsigned*>(fl + 16);    // 2 words
+            aws_.ticket = reinterpret_cast<unsigned*>(fl + 24);
+            const int64_t ncols = ffn + num_experts;
+            agg_ = torch::zeros({(int64_t)max_dispatch_ctas() * ncols}, torch::TensorOptions().dtype(torch::kInt64).device(torch::kCUDA, device_));
+            scratch_ = torch::zeros({(int64_t)capacity * (2 * top_k + ffn)}, i32);
+            int* s = scratch_.data_ptr<int>();
+            aws_.agg = reinterpret_cast<unsigned long long*>(agg_.data_ptr<int64_t>());
+            aws_.route_e = s;
+            aws_.route_pos = s + (size_t)capacity * top_k;
+            aws_.tok_slot = s + (size_t)capacity * top_k * 2;
+        }
+        rt_check(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+    }
+
+    ~NativeBuffer() {
+        try {
+            destroy();
+        } catch (...) {
+        }
+    }
+
+    // ---- heap exchange --------------------------------------------------------------
+    int64_t heap_bytes() const { return (int64_t)heap_->bytes(); }
+    int64_t mapped_bytes() const { return (int64_t)heap_->mapped_bytes(); }
+    int64_t local_ptr() const { return reinterpret_cast<int64_t>(heap_->local()); }
+    int export_fd() { return heap_->export_fd(); }
+    py::bytes export_ipc() { return py::bytes(heap_->export_ipc()); }
+    void import_peer_fd(int peer, int fd, int64_t mapped) {
+        check_peer(peer);
+        ctx_.peer[peer] = static_cast<char*>(heap_->import_fd(fd, (size_t)mapped));
+    }
+    void import_peer_ipc(int peer, const std::string& handle) {
+        check_peer(peer);
+        ctx_.peer[peer] = static_cast<char*>(heap_->import_ipc(handle));
+    }
+    void set_peer_ptr(int peer, int64_t ptr) {   // loopback world: all heaps live in this process
+        check_peer(peer);
+        ctx_.peer[peer] = reinterpret_cast<char*>(ptr);
+    }
+    bool peers_complete() const {
+        for (int i = 0; i < geo_.world; ++i)
+            if (!ctx_.peer[i]) return false;
+        return true;
+    }
+
+    // ---- collective-ish operations ---------------------------------------------------
+    void barrier() {
+        live();
+        rt_check(launch_barrier(ctx_, barrier_epoch_, stream()), "barrier launch");
+    }
+
+    void source_dispatch(const torch::Tensor& x, const c10::optional<torch::Tensor>& x_scale,
+                         const torch::Tensor& ids, const torch::Tensor& weights) {
+        live();
+        TORCH_CHECK(!is_ffn_, "source_dispatch runs on attention ranks");
+        const int T = (int)x.size(0);
+        TORCH_CHECK(T <= geo_.capacity, "more tokens than the registered capacity");
+        TORCH_CHECK(reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0, "x must be 16-byte aligned");
+        DispatchArgs a{};
+        a.x = x.data_ptr();
+        a.ids = reinterpret_cast<const long long*>(ids.data_ptr<int64_t>());
+        a.weights = weights.data_ptr<float>();
+        a.T = T;
+        if (geo_.fp8) {
+            TORCH_CHECK(x_scale.has_value(), "FP8 dispatch needs scales");
+            a.x_scale = x_scale->data_ptr<float>();
+            a.ss0 = x_scale->stride(0);
+            a.ss1 = x_scale->stride(1);
+        }
+        const LaunchShape s = dispatch_shape(geo_, T, num_sms_, max_smem_);
+        rt_check(launch_dispatch(ctx_, aws_, a, s, stream()), "dispatch launch");
+        ++launches_;
+    }
+
+    torch::Tensor source_collect(int64_t T) {
+        live();
+        TORCH_CHECK(!is_ffn_, "source_collect runs on attention ranks");
+        auto out = torch::empty({T, geo_.hidden}, torch::TensorOptions().dtype(torch::kBFloat16).device(torch::kCUDA, device_));
+        const LaunchShape s = collect_shape(geo_, (int)T, collect_sms_, max_smem_);
+        rt_check(launch_collect(ctx_, aws_, out.data_ptr(), (int)T, s, stream()), "collect launch");
+        ++launches_;
+        return out;
+    }
+
+    // Returns (recv_x, recv_scale or None, recv_weights, psum, host_counts, recv_src).
+    py::tuple worker_receive(int64_t rows_bound, bool read_host_counts, double cpu_timeout_s, bool col_major_scale) {
+        live();
+        TORCH_CHECK(is_ffn_, "worker_receive runs on FFN ranks");
+        auto dev = torch::TensorOptions().device(torch::kCUDA, device_);
+        const int EL = geo_.experts_local;
+        auto psum = torch::empty({EL}, dev.dtype(torch::kInt32));
+        ReceiveArgs r{};
+        r.psum = psum.data_ptr<int>();
+        std::vector<int64_t> host_counts;
+        int64_t rows = rows_bound;
+        if (read_host_counts) {
+            r.write_host_counts = 1;
+            r.rows_cap = (int)rows_bound;
+            volatile int* hc = reinterpret_cast<volatile int*>(static_cast<char*>(host_block_) + kHostCountsOff);
+            const int want = (int)(++host_seq_);
+            rt_check(launch_ffn_layout(ctx_, fws_, r, stream()), "layout launch");
+            ++launches_;
+            int seen = 0;
+            {
+                py::gil_scoped_release nogil;
+                const auto t0 = std::chrono::steady_clock::now();
+                while (true) {
+                    seen = hc[EL];
+                    if (seen == want || seen == -want) break;
+                    const double dt = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+                    if (dt > cpu_timeout_s) break;
+                    std::this_thread::yield();
+                }
+            }
+            if (seen != want) {
+                failed_ = true;
+                throw std::runtime_error(seen == -want ? "worker_receive: the device gave up waiting for source counts: " + status_text()
+                                                       : "worker_receive: timed out on the host waiting for receive counts");
+            }
+            rows = 0;
+            for (int e = 0; e < EL; ++e) {
+                host_counts.push_back(hc[e]);
+                rows += hc[e];
+            }
+            r.layout_ready = 1;
+            r.write_host_counts = 0;
+        }
+        auto recv_x = torch::empty({rows, geo_.hidden}, dev.dtype(geo_.fp8 ? torch::kFloat8_e4m3fn : torch::kBFloat16));
+        auto recv_w = torch::empty({rows}, dev.dtype(torch::kFloat32));
+        auto recv_src = torch::empty({rows, 2}, dev.dtype(torch::kInt32));
+        c10::optional<torch::Tensor> recv_scale;
+        if (geo_.fp8) {
+            const int64_t sg = geo_.scale_groups;
+            if (col_major_scale) {
+                const int64_t ld = (rows + 3) / 4 * 4;
+                recv_scale = torch::empty_strided({rows, sg}, {1, ld > 0 ? ld : 4}, dev.dtype(torch::kFloat32));
+            } else {
+                recv_scale = torch::empty({rows, sg}, dev.dtype(torch::kFloat32));
+            }
+            r.recv_scale = recv_scale->data_ptr<float>();
+            r.rs0 = recv_scale->stride(0);
+            r.rs1 = recv_scale->stride(1);
+        }
+        r.recv_x = recv_x.data_ptr();
+        r.recv_w = recv_w.data_ptr<float>();
+        r.recv_src = recv_src.data_ptr<int>();
+        r.rows_cap = (int)rows;
+        const LaunchShape s = receive_shape(geo_, ffn_sms_, max_smem_);
+        rt_check(launch_receive(ctx_, fws_, r, s, stream()), "receive launch");
+        ++launches_;
+        py::object scale_obj = recv_scale.has_value() ? py::cast(*recv_scale) : py::none();
+        return py::make_tuple(recv_x, scale_obj, recv_w, psum, host_counts, recv_src);
+    }
+
+    void worker_reply(const torch::Tensor& rows) {
+        live();
+        TORCH_CHECK(is_ffn_, "worker_reply runs on FFN ranks");
+        TORCH_CHECK(reinterpret_cast<uintptr_t>(rows.data_ptr()) % 16 == 0, "rows must be 16-byte aligned");
+        const LaunchShape s = reply_shape(geo_, ffn_sms_, max_smem_);
+        rt_check(launch_reply(ctx_, fws_, rows.data_ptr(), (int)rows.size(0), s, stream()), "reply launch");
+        ++launches_;
+    }
+
+    // ---- status -----------------------------------------------------------------------
+    py::dict status() {
+        const volatile Status* s = static_cast<const volatile Status*>(host_block_);
+        py::dict d;
+        const int code = s->code;
+        d["code"] = code;
+        d["text"] = std::string(code_name(code));
+        d["kernel"] = s->kernel;
+        d["rank"] = s->rank;
+        d["peer"] = s->peer;
+        d["epoch"] = s->epoch;
+        d["expected"] = s->expected;
+        d["observed"] = s->observed;
+        d["detail0"] = s->detail0;
+        d["detail1"] = s->detail1;
+        d["fatal"] = code != kOk && code != kBadRoute;
+        return d;
+    }
+    int status_code() const { return static_cast<const volatile Status*>(host_block_)->code; }
+
+    // After a non-fatal report (an illegal route): forget it so the next one is recorded.
+    void clear_status() {
+        rt_check(cudaStreamSynchronize(stream()), "cudaStreamSynchronize");
+        std::memset(host_block_, 0, sizeof(Status));
+        rt_check(cudaMemsetAsync(ctx_.poison, 0, 4 * sizeof(int), stream()), "cudaMemsetAsync");
+        rt_check(cudaStreamSynchronize(stream()), "cudaStreamSynchronize");
+    }
+    int bad_routes() {
+        int v = 0;
+        rt_check(cudaMemcpy(&v, ctx_.poison + 2, sizeof(int), cudaMemcpyDeviceToHost), "cudaMemcpy");
+        return v;
+    }
+
+    int64_t launches() const { return launches_; }
+    int resolved_num_sms() const { return num_sms_; }
+    int device_sms() const { return device_sms_; }
+    int64_t record_bytes() const { return geo_.rec_bytes; }
+
+    void destroy() {
+        if (destroyed_) return;
+        destroyed_ = true;
+        cudaSetDevice(device_);
+        cudaDeviceSynchronize();
+        flags_ = torch::Tensor();
+        scratch_ = torch::Tensor();
+        agg_ = torch::Tensor();
+        heap_->release();
+        if (host_block_) cudaFreeHost(host_block_);
+        host_block_ = nullptr;
+    }
+
+private:
+    static constexpr size_t kHostBlockBytes = 8192;
+    static constexpr size_t kHostCountsOff = 1024;
+
+    cudaStream_t stream() const { return at::cuda::getCurrentCUDAStream(device_).stream(); }
+    void live() const {
+        TORCH_CHECK(!destroyed_, "buffer is closed");
+        TORCH_CHECK(peers_complete(), "peer heaps have not been connected");
+    }
+    void check_peer(int peer) const { TORCH_CHECK(peer >= 0 && peer < geo_.world, "peer out of range"); }
+    std::string status_text() {
+        const volatile Status* s = static_cast<const volatile Status*>(host_block_);
+        return std::string(code_name(s->code)) + " (rank " + std::to_string(s->rank) + ", peer " + std::to_string(s->peer) + ")";
+    }
+
+    int rank_, role_rank_ = 0, device_ = 0, device_sms_ = 0, max_smem_ = 0;
+    int num_sms_, collect_sms_, ffn_sms_;
+    bool is_ffn_ = false, destroyed_ = false, failed_ = false;
+    Geometry geo_{};
+    RankCtx ctx_{};
+    AttnWs aws_{};
+    FfnWs fws_{};
+    unsigned* barrier_epoch_ = nullptr;
+    std::unique_ptr<SymmetricHeap> heap_;
+    void* host_block_ = nullptr;
+    torch::Tensor flags_, scratch_, agg_;
+    int64_t host_seq_ = 0, launches_ = 0;
+};
+
+}  // namespace afdep
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+    using afdep::NativeBuffer;
+    m.doc() = "afdep_b200 native runtime (sm_100a)";
+    m.attr("max_ranks") = afdep::kMaxRanks;
+    m.def("vmm_supported", [](int device) { return afdep::SymmetricHeap::vmm_supported(device); });
+    py::class_<NativeBuffer>(m, "NativeBuffer")
+        .def(py::init<int, int, int, int, int, int, int, bool, int, int, int, int, double, int64_t, const std::string&, bool>(),
+             py::arg("rank"), py::arg("ffn"), py::arg("attn"), py::arg("hidden"), py::arg("top_k"), py::arg("num_experts"),
+             py::arg("capacity"), py::arg("fp8"), py::arg("alignment"), py::arg("num_sms"), py::arg("collect_sms"),
+             py::arg("ffn_sms"), py::arg("gpu_timeout_s"), py::arg("aux_bytes"), py::arg("heap_mode"), py::arg("bounds_check"))
+        .def("heap_bytes", &NativeBuffer::heap_bytes)
+        .def("mapped_bytes", &NativeBuffer::mapped_bytes)
+        .def("local_ptr", &NativeBuffer::local_ptr)
+        .def("export_fd", &NativeBuffer::export_fd)
+        .def("export_ipc", &NativeBuffer::export_ipc)
+        .def("import_peer_fd", &NativeBuffer::import_peer_fd)
+        .def("import_peer_ipc", &NativeBuffer::import_peer_ipc)
+        .def("set_peer_ptr", &NativeBuffer::set_peer_ptr)
+        .def("peers_complete", &NativeBuffer::peers_complete)
+        .def("barrier", &NativeBuffer::barrier)
+        .def("source_dispatch", &NativeBuffer::source_dispatch)
+        .def("source_collect", &NativeBuffer::source_collect)
+        .def("worker_receive", &NativeBuffer::worker_receive)
+        .def("worker_reply", &NativeBuffer::worker_reply)
+        .def("status", &NativeBuffer::status)
+        .def("status_code", &NativeBuffer::status_code)
+        .def("clear_status", &NativeBuffer::clear_status)
+        .def("bad_routes", &NativeBuffer::bad_routes)
+        .def("launches", &NativeBuffer::launches)
+        .def("resolved_num_sms", &NativeBuffer::resolved_num_sms)
+        .def("device_sms", &NativeBuffer::device_sms)
+        .def("record_bytes", &NativeBuffer::record_bytes)
+        .def("destroy", &NativeBuffer::destroy);
+}

@@ -1,0 +1,216 @@
+"""The product transport: sm_100a kernels over a symmetric heap mapped into every peer.
+
+Construction is collective: every rank allocates its heap (CUDA virtual memory exported as a
+file descriptor, or a cudaIpc handle when that is unavailable), hands it to every peer over
+the control plane, maps the peers' heaps, and meets in a device-side barrier.  After that no
+call on the hot path touches the host side of another rank: the four role calls each launch
+one kernel (two for ``read_host_counts=True``) on the caller's current stream.
+"""
+
+from __future__ import annotations
+
+import os
+
+from ..buffer import AfdepRouteError, AfdepTimeoutError
+from ..config import NATIVE_MAX_RANKS, Config
+
+
+def _env_int(name: str, default: int) -> int:
+    value = os.environ.get(name)
+    return int(value) if value else default
+
+
+class NativeTransport:
+    def __init__(self, *, control, group, config: Config, num_sms: int, options: dict) -> None:
+        import torch
+
+        from .._native import load_native
+
+        if config.world_size > NATIVE_MAX_RANKS:
+            raise ValueError(f"the native transport spans one NVLink domain of at most {NATIVE_MAX_RANKS} ranks")
+        self._torch, self._control, self.config = torch, control, config
+        self._native = load_native()
+        self.device = torch.cuda.current_device()
+        self.topk_idx_dtype = torch.int64
+        self.payload_dtype = torch.float8_e4m3fn if config.is_fp8 else torch.bfloat16
+        self.float32, self.bfloat16 = torch.float32, torch.bfloat16
+        self._failed: str | None = None
+        self._loopback = bool(options.get("loopback", False))
+        self._col_major_scale = options.get("recv_scale_layout", "row_major") == "col_major_tma"
+
+        timeout_s = float(config.gpu_timeout_s)
+        if os.environ.get("AFDEP_TIMEOUT_MS"):
+            timeout_s = float(os.environ["AFDEP_TIMEOUT_MS"]) / 1000.0
+        if "gpu_timeout_s" in options:
+            timeout_s = float(options["gpu_timeout_s"])
+        sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        collect_sms = int(options.get("collect_sms", _env_int("AFDEP_COLLECT_SMS", 0))) or min(sm_count, 2 * num_sms)
+        ffn_sms = int(options.get("ffn_sms", _env_int("AFDEP_FFN_SMS", 0))) or sm_count
+        bounds = bool(int(os.environ.get("AFDEP_BOUNDS_CHECK", "1")))
+
+        mode = options.get("heap_mode") or os.environ.get("AFDEP_HEAP_MODE")
+        if self._loopback:
+            mode = "plain"
+        elif mode is None:
+            mode = "vmm" if self._native.vmm_supported(self.device) else "ipc"
+            modes = control.all_gather(mode)
+            if any(m != "vmm" for m in modes):
+                mode = "ipc"
+        self.heap_mode = mode
+        self._nb = self._native.NativeBuffer(
+            rank=control.rank,
+            ffn=config.ffn_ranks,
+            attn=config.attention_ranks,
+            hidden=config.hidden_size,
+            top_k=config.top_k,
+            num_experts=config.num_experts,
+            capacity=config.capacity_tokens_per_rank,
+            fp8=config.is_fp8,
+            alignment=config.expert_alignment,
+            num_sms=num_sms,
+            collect_sms=collect_sms,
+            ffn_sms=ffn_sms,
+            gpu_timeout_s=timeout_s,
+            aux_bytes=int(options.get("aux_bytes", 0)),
+            heap_mode=mode,
+            bounds_check=bounds,
+        )
+        self.num_buffer_bytes = int(self._nb.heap_bytes())
+        self.num_sms = num_sms
+        self.is_ffn = control.rank < config.ffn_ranks
+        self._empty = None
+        if not self._loopback:
+            self._connect_peers()
+            torch.cuda.synchronize(self.device)
+            control.barrier()
+            self._nb.barrier()
+            torch.cuda.synchronize(self.device)
+            self.raise_status()
+
+    # ---- bring-up ---------------------------------------------------------------------
+    def _connect_peers(self) -> None:
+        control, nb = self._control, self._nb
+        sizes = control.all_gather(int(nb.mapped_bytes()))
+        if self.heap_mode == "vmm":
+            from .fd_exchange import exchange_fds
+
+            my_fd = nb.export_fd()
+            fds = exchange_fds(control, my_fd)
+            try:
+                for peer, fd in enumerate(fds):
+                    if peer != control.rank:
+                        nb.import_peer_fd(peer, fd, sizes[peer])
+            finally:
+                for fd in fds:
+                    if fd >= 0:
+                        os.close(fd)
+        elif self.heap_mode == "ipc":
+            handles = control.all_gather(bytes(nb.export_ipc()))
+            for peer, handle in enumerate(handles):
+                if peer != control.rank:
+                    nb.import_peer_ipc(peer, handle)
+        else:
+            raise ValueError("a multi-process buffer needs heap_mode 'vmm' or 'ipc'")
+
+    def wire_loopback(self, peers: list["NativeTransport"]) -> None:
+        """Loopback world: all heaps live in this process; exchange raw pointers."""
+        for peer, other in enumerate(peers):
+            if other is not self:
+                self._nb.set_peer_ptr(peer, other._nb.local_ptr())
+
+    # ---- small queries ----------------------------------------------------------------
+    @property
+    def comm_stream(self):
+        return self._torch.cuda.current_stream(self.device)
+
+    def check_device(self) -> None:
+        if self._torch.cuda.current_device() != self.device:
+            raise RuntimeError("afdep buffer used on a different CUDA device")
+
+    def is_capturing(self) -> bool:
+        return self._torch.cuda.is_current_stream_capturing()
+
+    def on_device(self, tensor) -> bool:
+        return bool(tensor.is_cuda) and tensor.get_device() == self.device
+
+    def raise_status(self) -> None:
+        if self._failed:
+            raise AfdepTimeoutError(self._failed)
+        if self._nb.status_code() == 0 or self.is_capturing():
+            return
+        st = self._nb.status()
+        if st["fatal"]:
+            self._failed = (
+                f"device wait abandoned on rank {st['rank']}: {st['text']} (kernel {st['kernel']}, peer {st['peer']}, "
+                f"epoch {st['epoch']}, expected {st['expected']}, observed {st['observed']}); close the buffer"
+            )
+            raise AfdepTimeoutError(self._failed)
+        n = self._nb.bad_routes()
+        self._nb.clear_status()
+        raise AfdepRouteError(
+            f"{n} illegal route(s): first at token {st['expected']}, choice {st['detail0']}, expert id {st['observed']}; "
+            "the affected tokens were not dispatched and collect as zero rows"
+        )
+
+    def stats(self) -> dict:
+        return {
+            "backend": "native",
+            "heap_mode": self.heap_mode,
+            "registered_bytes": self.num_buffer_bytes,
+            "record_bytes": int(self._nb.record_bytes()),
+            "launches": int(self._nb.launches()),
+            "num_sms": int(self._nb.resolved_num_sms()),
+            "status": dict(self._nb.status()),
+        }
+
+    # ---- role operations --------------------------------------------------------------
+    def _empties(self):
+        if self._empty is None:
+            torch, c = self._torch, self.config
+            dev = torch.device("cuda", self.device)
+            self._empty = {
+                "x": torch.empty((0, c.hidden_size), dtype=self.payload_dtype, device=dev),
+                "scale": torch.empty((0, c.scale_groups), dtype=torch.float32, device=dev) if c.is_fp8 else None,
+                "ids": torch.empty((0, c.top_k), dtype=torch.int64, device=dev),
+                "w": torch.empty((0, c.top_k), dtype=torch.float32, device=dev),
+                "out": torch.empty((0, c.hidden_size), dtype=torch.bfloat16, device=dev),
+                "recv_w": torch.empty((0,), dtype=torch.float32, device=dev),
+                "psum": torch.zeros((c.experts_per_rank,), dtype=torch.int32, device=dev),
+                "src": torch.empty((0, 2), dtype=torch.int32, device=dev),
+            }
+        return self._empty
+
+    def empty_source(self):
+        e = self._empties()
+        return e["x"], e["scale"], e["ids"], e["w"]
+
+    def empty_receive(self):
+        e = self._empties()
+        return e["x"], e["scale"], e["recv_w"], e["psum"], e["src"]
+
+    def empty_output(self):
+        return self._empties()["out"]
+
+    def source_dispatch(self, x, x_scale, ids, weights, *, bucket: int) -> None:
+        self._nb.source_dispatch(x, x_scale, ids, weights)
+
+    def source_collect(self, num_tokens: int):
+        return self._nb.source_collect(num_tokens)
+
+    def worker_receive(self, *, bucket: int, read_host_counts: bool):
+        rows = self.config.receive_rows(bucket)
+        return self._nb.worker_receive(rows, read_host_counts, float(self.config.cpu_timeout_s), self._col_major_scale)
+
+    def worker_reply(self, rows) -> None:
+        self._nb.worker_reply(rows)
+
+    def close(self) -> None:
+        torch = self._torch
+        torch.cuda.synchronize(self.device)
+        if not self._loopback:
+            self._control.barrier()
+            if not self._failed and self._nb.status_code() in (0, 16):
+                self._nb.barrier()
+                torch.cuda.synchronize(self.device)
+            self._control.barrier()
+        self._nb.destroy()

@@ -1,0 +1,392 @@
+"""Headline benchmark: dispatch + combine of one AFD expert-parallel exchange.
+
+    python bench.py --gpus N --steps K --warmup W [--impl ours|nccl|reference] [--config weak|2|3|4]
+
+N = 1 runs one attention and one FFN rank colocated on a single GPU (all ranks in this
+process); N >= 2 expects one process per GPU (torchrun) and splits the ranks N/2 FFN + N/2
+attention (6 attention + 2 FFN for ``--config 4``).  A step is one complete exchange through
+the public role API: ``source_dispatch`` -> ``worker_receive`` -> ``worker_reply`` ->
+``source_collect``.  The FFN "expert" is the identity on a preallocated BF16 tensor, so the
+timed region holds the library's four kernels and nothing else.
+
+Every step is bracketed by CUDA events on the launching stream after a device-side barrier
+across ranks (outside the events); L2 is flushed between steps; the reported time is the
+maximum over ranks.  ``value`` is the job's aggregate wire throughput: bytes that cross NVLink
+in both directions (one record per token and destination FFN rank out, one BF16 row back)
+divided by the step time.  The ``e2e`` entry repeats the measurement with, inside the timed
+region, the host->device copy of the step's inputs from pinned memory and a device->host read
+of a checksum of the result.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+CONFIGS = {
+    # name: hidden, experts per FFN rank, top_k, tokens per attention rank, payload, routing
+    "weak": dict(hidden=4096, experts_per_ffn=64, top_k=8, tokens=2048, payload="bf16", zipf=None),
+    "2": dict(hidden=4096, experts_per_ffn=64, top_k=8, tokens=2048, payload="bf16", zipf=None),
+    "3": dict(hidden=7168, experts_per_ffn=64, top_k=8, tokens=4096, payload="fp8", zipf=1.1),
+    "4": dict(hidden=7168, experts_per_ffn=128, top_k=8, tokens=128, payload="bf16", zipf=None),
+}
+
+
+def parse_args():
+    p = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=50)
+    p.add_argument("--warmup", type=int, default=5)
+    p.add_argument("--impl", choices=("ours", "nccl", "reference"), default="ours")
+    p.add_argument("--config", choices=tuple(CONFIGS), default="weak")
+    p.add_argument("--tokens", type=int, default=0, help="override tokens per attention rank")
+    p.add_argument("--num-sms", type=int, default=0)
+    p.add_argument("--graph", action="store_true", help="replay each step from a CUDA graph")
+    p.add_argument("--no-e2e", action="store_true")
+    return p.parse_args()
+
+
+def topology(n: int, config: str) -> tuple[int, int]:
+    if n == 1:
+        return 1, 1
+    if config == "4" and n == 8:
+        return 2, 6
+    return n // 2, n - n // 2
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs (read-only)."""
+
+    QUERY = (
+        "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+        "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+    )
+
+    def __init__(self, device_index: int) -> None:
+        self.proc, self.index = None, device_index
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                stdout=subprocess.PIPE,
+                stderr=subprocess.DEVNULL,
+                text=True,
+            )
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.splitlines():
+            f = [s.strip() for s in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {
+            "sm_mhz": statistics.median(sm) if sm else None,
+            "sm_max_mhz": max(mx) if mx else None,
+            "samples": len(sm),
+            "reasons": sorted(reasons),
+        }
+
+
+def reference_arm(args) -> None:
+    """The unmodified reference cannot run on this pool; say why in one line."""
+    rank = int(os.environ.get("RANK", "0"))
+    reason = None
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if args.gpus < 2:
+        reason = "the reference needs at least two ranks (afdep/deepep.py:218-221); there is no 1-GPU mode"
+    elif not os.path.isdir(os.path.join(ref, "afdep")):
+        reason = (
+            "closed on this pool: the reference's source calls a batched-memcpy CUDA entry point that is closed here "
+            "(csrc/elastic/buffer.hpp:439), so its install under baseline/_ref cannot be carried to the GPU box"
+        )
+    else:
+        probe = (
+            "import sys; sys.path.insert(0, %r); from afdep._build import load_deepep; load_deepep(); print('built')" % ref
+        )
+        try:
+            out = subprocess.run([sys.executable, "-c", probe], capture_output=True, text=True, timeout=900)
+            if out.returncode != 0:
+                tail = (out.stderr.strip().splitlines() or ["build failed"])[-1]
+                reason = "reference extension does not build here (needs NCCL >= 2.30.7 device API): " + tail[:200]
+            else:
+                reason = "reference built, but its run-time JIT shells out to cuobjdump for every kernel, which is not allowed here"
+        except subprocess.TimeoutExpired:
+            reason = "reference extension build timed out"
+    if rank == 0:
+        print(json.dumps({"impl": "reference", "unavailable": reason}))
+
+
+def main() -> None:
+    args = parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from afdep_b200 import Buffer, Config
+    from afdep_b200.utils import synthetic
+
+    n = args.gpus
+    spec = dict(CONFIGS[args.config])
+    if args.tokens:
+        spec["tokens"] = args.tokens
+    ffn, attn = topology(n, args.config)
+    T = spec["tokens"]
+    cfg = Config(
+        T,
+        spec["hidden"],
+        spec["experts_per_ffn"] * ffn,
+        spec["top_k"],
+        ffn,
+        attn,
+        payload=spec["payload"],
+        num_sms=args.num_sms,
+        gpu_timeout_s=20,
+        cpu_timeout_s=60,
+    )
+    multi = n > 1
+    if multi:
+        rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+        assert world == n, "launch with torchrun --nproc-per-node equal to --gpus"
+        local = int(os.environ.get("LOCAL_RANK", rank))
+        torch.cuda.set_device(local)
+        import datetime
+
+        dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=600))
+        backend = "native" if args.impl == "ours" else "nccl"
+        buffers = [Buffer(group=dist.group.WORLD, config=cfg, backend=backend)]
+    else:
+        rank, local = 0, 0
+        torch.cuda.set_device(0)
+        if args.impl != "ours":
+            print(json.dumps({"impl": args.impl, "unavailable": "the NCCL baseline needs at least two ranks"}))
+            return
+        from afdep_b200.parallel.loopback import LoopbackWorld
+
+        world_obj = LoopbackWorld(cfg, gpu_timeout_s=20.0)
+        buffers = world_obj.buffers
+    dev = torch.device("cuda", local)
+
+    # ---- per-rank state: pinned host inputs, device inputs, identity-expert rows ----------
+    state = []
+    for buf in buffers:
+        s = {"buf": buf}
+        if buf.role == "attention":
+            x, ids, w, scale = synthetic.random_batch(cfg, T, seed=1000 + buf.role_rank, zipf_s=spec["zipf"])
+            s["host"] = [t.pin_memory() if t is not None else None for t in (x, ids, w, scale)]
+            s["dev"] = [t.to(dev) if t is not None else None for t in s["host"]]
+            s["ids_cpu"] = ids
+        else:
+            s["rows"] = torch.zeros((cfg.receive_rows(T), cfg.hidden_size), dtype=torch.bfloat16, device=dev)
+        state.append(s)
+
+    # wire bytes per step (both directions) from the routes: one record per (token, FFN rank)
+    el = cfg.experts_per_rank
+    records = 0
+    for s in state:
+        if "ids_cpu" in s:
+            ids = s["ids_cpu"]
+            dest = torch.where(ids >= 0, ids // el, torch.full_like(ids, -1))
+            for f in range(ffn):
+                records += int((dest == f).any(dim=1).sum())
+    if multi:
+        allrec = [None] * n
+        dist.all_gather_object(allrec, records)
+        records = sum(allrec)
+    row_out = cfg.hidden_size * (1 if cfg.is_fp8 else 2) + (cfg.scale_groups * 4 if cfg.is_fp8 else 0)
+    wire_bytes = records * (row_out + cfg.hidden_size * 2)
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    ordered = sorted(state, key=lambda s: 0 if s["buf"].role == "attention" else 1)
+
+    def barrier_all():
+        if multi:
+            buffers[0]._t._nb.barrier() if args.impl == "ours" else dist.barrier()
+
+    def step(copy_inputs: bool):
+        """One exchange in dependency order; returns a device checksum on attention ranks."""
+        result = None
+        for s in ordered:
+            if s["buf"].role == "attention":
+                if copy_inputs:
+                    for d, h in zip(s["dev"], s["host"]):
+                        if d is not None:
+                            d.copy_(h, non_blocking=True)
+                x, ids, w, scale = s["dev"]
+                s["buf"].source_dispatch(x, ids, w, scale, bucket=T)
+        for s in ordered:
+            if s["buf"].role == "ffn":
+                rec = s["buf"].worker_receive(bucket=T)
+                rows = rec.recv_x if not cfg.is_fp8 else s["rows"]
+                s["psum"] = rec.recv_count_psum
+                s["buf"].worker_reply(rows, rec.receipt)
+        for s in ordered:
+            if s["buf"].role == "attention":
+                s["out"] = s["buf"].source_collect()
+                result = s["out"]
+        return result
+
+    graph = None
+    if args.graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                step(False)
+        torch.cuda.synchronize()
+        if multi:
+            dist.barrier()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            step(False)
+        torch.cuda.current_stream().wait_stream(side)
+
+    def timed(copy_inputs: bool, steps: int, warmup: int):
+        times, phases = [], []
+        host_result = torch.zeros(1, dtype=torch.float32).pin_memory()
+        for i in range(warmup + steps):
+            flush.fill_(i & 0xFF)
+            barrier_all()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            if graph is not None and not copy_inputs:
+                graph.replay()
+            else:
+                out = step(copy_inputs)
+                if copy_inputs:
+                    src = out.float().sum().reshape(1) if out is not None else state[0]["psum"].float().sum().reshape(1)
+                    host_result.copy_(src, non_blocking=True)
+            e1.record()
+            e1.synchronize()
+            if i >= warmup:
+                times.append(e0.elapsed_time(e1))
+        return times
+
+    torch.cuda.synchronize()
+    if multi:
+        dist.barrier()
+    launches_before = sum(int(s["buf"].stats().get("launches", 0)) for s in state)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    torch.cuda.synchronize()
+    t_wall0 = time.perf_counter()
+    times = timed(False, args.steps, args.warmup)
+    torch.cuda.synchronize()
+    t_wall1 = time.perf_counter()
+    clocks = sampler.stop() if rank == 0 else None
+    launches_after = sum(int(s["buf"].stats().get("launches", 0)) for s in state)
+    launches = (launches_after - launches_before) * args.steps // (args.steps + args.warmup)
+    e2e_times = None
+    if not args.no_e2e:
+        e2e_times = timed(True, args.steps, max(3, args.warmup))
+
+    def reduce_max(values):
+        total = sum(values)
+        if multi:
+            allv = [None] * n
+            dist.all_gather_object(allv, total)
+            return max(allv)
+        return total
+
+    total_ms = reduce_max(times)
+    ms_per_step = total_ms / args.steps
+    if multi:
+        alll = [None] * n
+        dist.all_gather_object(alll, launches)
+        launches = sum(alll)
+    value = wire_bytes / (ms_per_step * 1e-3) / 1e9
+    result = {
+        "metric": "dispatch+combine aggregate wire GB/s (all ranks, max-over-ranks step time)",
+        "value": round(value, 3),
+        "unit": "GB/s",
+        "n_gpus": n,
+        "steps": args.steps,
+        "warmup": args.warmup,
+        "ms_per_step": round(ms_per_step, 5),
+        "us_per_exchange": round(ms_per_step * 1e3, 2),
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "fp8(e4m3)+bf16" if cfg.is_fp8 else "bf16",
+        "data": "synthetic (seeded N(0,1) activations, distinct top-k routes, softmax weights; no weights involved)",
+        "impl": args.impl,
+        "config": {
+            "model": f"AFD MoE exchange, BASELINE config {args.config}",
+            "global_batch": T * attn,
+            "seq_len": 1,
+            "parallelism": f"{attn}A+{ffn}F" + (" colocated on one GPU" if not multi else ""),
+            "hidden": cfg.hidden_size,
+            "num_experts": cfg.num_experts,
+            "top_k": cfg.top_k,
+            "tokens_per_attention_rank": T,
+            "payload": cfg.payload,
+            "routing": "zipf(1.1)" if spec["zipf"] else "uniform",
+            "l2": "flushed between steps (256 MiB fill)",
+            "mode": "cuda-graph replay" if graph is not None else "eager",
+            "wire_bytes_per_step": wire_bytes,
+            "tokens_per_s": round(T * attn / (ms_per_step * 1e-3), 1),
+            "per_attention_rank_GBs": round(value / attn, 3),
+        },
+        "clocks": clocks,
+        "gpu_launches": launches,
+        "wall_s_timed_region": round(t_wall1 - t_wall0, 3),
+    }
+    if e2e_times is not None:
+        e2e_ms = reduce_max(e2e_times) / args.steps
+        hi = sum(sum(t.numel() * t.element_size() for t in s["host"] if t is not None) for s in state if "host" in s)
+        if multi:
+            allh = [None] * n
+            dist.all_gather_object(allh, hi)
+            hi = sum(allh)
+        result["e2e"] = {
+            "value": round(wire_bytes / (e2e_ms * 1e-3) / 1e9, 3),
+            "unit": "GB/s",
+            "ms_per_step": round(e2e_ms, 5),
+            "h2d_bytes_per_step": hi,
+            "d2h_bytes_per_step": 4 * n,
+        }
+    for s in state:
+        s["buf"].check()
+    if multi:
+        buffers[0].close()
+        dist.barrier()
+        dist.destroy_process_group()
+    else:
+        world_obj.close()
+    if rank == 0:
+        print(json.dumps(result))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,96 @@
+"""Four CPU ranks over Gloo: the role API end to end on the pure-torch transport.
+
+Covers the first benchmark configuration (2 FFN + 2 attention ranks, hidden 128*, 8 experts,
+top-2, 16 tokens, bucket 16; *hidden is 256 here because the API requires multiples of 256)
+with the closed form ``out == sum_k w_k * (e_k + 1) * x``, plus the host-side rules of the
+Buffer that the reference checks with mocks: single pending exchange, receipt identity,
+collective close.
+"""
+
+import pytest
+import torch
+
+from afdep_b200 import Buffer, Config
+from afdep_b200.utils import oracle, synthetic
+from tests._dist import run_ranks
+
+
+def _exchange(rank, world, payload, read_host_counts):
+    import torch.distributed as dist
+
+    cfg = Config(16, 256, 8, 2, 2, 2, expert_alignment=4, payload=payload)
+    buf = Buffer(group=dist.group.WORLD, config=cfg, backend="gloo")
+    assert buf.role == ("ffn" if rank < 2 else "attention")
+    for epoch in range(3):
+        batches = [synthetic.exact_batch(cfg, 16, a, epoch, active=16 - 5 * a * (epoch % 2)) for a in range(2)]
+        if buf.role == "attention":
+            x, ids, w, scale = batches[buf.role_rank]
+            buf.source_dispatch(x, ids, w, scale, bucket=16, read_host_counts=read_host_counts)
+            with pytest.raises(RuntimeError, match="previous exchange"):
+                buf.source_dispatch(x, ids, w, scale, bucket=16)
+            out = buf.source_collect()
+            factor = torch.where(ids >= 0, (ids + 1).float() * w, torch.zeros_like(w)).sum(dim=1)
+            expect = (oracle.dequantize(x, scale) * factor[:, None]).to(torch.bfloat16)
+            torch.testing.assert_close(out, expect, rtol=0, atol=0)
+            torch.testing.assert_close(out, oracle.expected_combine(cfg, oracle.SourceBatch(x, ids, w, scale)), rtol=0, atol=0)
+        else:
+            rec = buf.worker_receive(bucket=16, read_host_counts=read_host_counts)
+            exp = oracle.expected_receive(cfg, buf.role_rank, [oracle.SourceBatch(*b[:3], b[3]) for b in batches], rows=rec.recv_x.shape[0])
+            assert torch.equal(rec.recv_count_psum.long(), exp.layout.ends)
+            v = exp.valid
+            assert torch.equal(rec.recv_x[v].float(), exp.recv_x[v].float())
+            assert torch.equal(rec.recv_topk_weights[v], exp.recv_weights[v])
+            assert torch.equal(rec.handle.recv_src_metadata[v], exp.recv_src[v])
+            if read_host_counts:
+                assert rec.recv_counts_host == exp.layout.aligned_counts
+                assert rec.recv_x.shape[0] == exp.layout.rows_exact
+            else:
+                assert rec.recv_x.shape[0] == cfg.receive_rows(16)
+            rows = oracle.synthetic_expert_rows(cfg, buf.role_rank, rec.recv_x, rec.recv_scale, rec.recv_topk_weights, rec.recv_count_psum)
+            with pytest.raises(ValueError, match="Handle does not belong"):
+                buf.worker_reply(rows, type(rec.receipt)(**{**rec.receipt.__dict__, "_owner": object()}))
+            buf.worker_reply(rows, rec.receipt)
+    buf.close()
+    buf.close()   # idempotent
+
+
+@pytest.mark.parametrize("payload", ["bf16", "fp8"])
+@pytest.mark.parametrize("read_host_counts", [False, True])
+def test_four_rank_exchange(payload, read_host_counts):
+    run_ranks(_exchange, 4, payload, read_host_counts)
+
+
+def _mismatch(rank, world):
+    import torch.distributed as dist
+
+    cfg = Config(16, 256, 8, 2, 2, 2, expert_alignment=4 if rank else 8)
+    with pytest.raises(ValueError, match="same Config"):
+        Buffer(group=dist.group.WORLD, config=cfg, backend="gloo")
+
+
+def test_configs_must_agree():
+    run_ranks(_mismatch, 4)
+
+
+def _pending_close(rank, world):
+    import torch.distributed as dist
+
+    cfg = Config(8, 256, 8, 2, 2, 2, expert_alignment=1)
+    buf = Buffer(group=dist.group.WORLD, config=cfg, backend="gloo")
+    batch = synthetic.exact_batch(cfg, 8, 0, 0)
+    if buf.role == "attention":
+        buf.source_dispatch(*batch[:3], bucket=8)
+        with pytest.raises(RuntimeError, match="requires the ffn role"):
+            buf.worker_receive(bucket=8)
+    rec = buf.worker_receive(bucket=8) if buf.role == "ffn" else None
+    with pytest.raises(RuntimeError, match="pending exchange"):
+        buf.close()
+    if rec is not None:
+        buf.worker_reply(torch.zeros(rec.receipt.recv_shape, dtype=torch.bfloat16), rec.receipt)
+    else:
+        buf.source_collect()
+    buf.close()
+
+
+def test_close_refuses_pending_exchange_on_every_rank():
+    run_ranks(_pending_close, 4)

@@ -1,0 +1,237 @@
+"""The CUDA transport on ONE GPU: every rank of a Buffer inside this process.
+
+Each case runs complete exchanges through the public role API and compares what the FFN
+ranks receive and what the attention ranks collect with the pure-torch oracle: bit for bit,
+because the transport is deterministic and the inputs are exactly representable.
+"""
+
+import pytest
+import torch
+
+from afdep_b200 import AfdepRouteError, Config
+from afdep_b200.utils import oracle, synthetic
+
+pytestmark = pytest.mark.gpu
+
+
+def to_dev(batch):
+    return tuple(None if t is None else t.cuda() for t in batch)
+
+
+def make_world(cfg, **options):
+    from afdep_b200.parallel.loopback import LoopbackWorld
+
+    return LoopbackWorld(cfg, gpu_timeout_s=2.0, **options)
+
+
+def run_and_check(world, cfg, batches, *, bucket=None, read_host_counts=False, exact=True):
+    dev = [to_dev(b) for b in batches]
+    sources = [oracle.SourceBatch(b[0], b[1], b[2], b[3]) for b in batches]
+
+    def expert(i, rec):
+        return oracle.synthetic_expert_rows(cfg, i, rec.recv_x, rec.recv_scale, rec.recv_topk_weights, rec.recv_count_psum)
+
+    outs, received = world.exchange(dev, expert, bucket=bucket, read_host_counts=read_host_counts)
+    torch.cuda.synchronize()
+    for b in world.buffers:
+        b.check()
+    for f, rec in enumerate(received):
+        exp = oracle.expected_receive(cfg, f, sources, rows=rec.recv_x.shape[0])
+        assert torch.equal(rec.recv_count_psum.cpu().long(), exp.layout.ends), f"ends differ on FFN rank {f}"
+        v = exp.valid
+        assert torch.equal(rec.recv_x.cpu()[v].float(), exp.recv_x[v].float())
+        assert torch.equal(rec.recv_topk_weights.cpu()[v], exp.recv_weights[v])
+        assert torch.equal(rec.handle.recv_src_metadata.cpu()[v], exp.recv_src[v])
+        if cfg.is_fp8:
+            assert torch.equal(rec.recv_scale.cpu()[v], exp.recv_scale[v])
+        if read_host_counts:
+            assert rec.recv_counts_host == exp.layout.aligned_counts
+            assert rec.recv_x.shape[0] == exp.layout.rows_exact
+        else:
+            assert rec.recv_x.shape[0] == cfg.receive_rows(bucket or cfg.capacity_tokens_per_rank)
+    for a, out in enumerate(outs):
+        expect = oracle.expected_combine(cfg, sources[a])
+        if exact:
+            assert torch.equal(out.cpu().float(), expect.float()), f"combine differs on attention rank {a}"
+        else:
+            torch.testing.assert_close(out.cpu().float(), expect.float(), rtol=2e-2, atol=2e-2)
+    return outs, received
+
+
+@pytest.mark.parametrize("payload", ["bf16", "fp8"])
+@pytest.mark.parametrize("ffn,attn,experts,top_k", [(1, 1, 8, 2), (2, 2, 8, 2), (2, 2, 16, 8), (4, 4, 32, 8), (2, 6, 64, 6)])
+def test_exact_exchange(payload, ffn, attn, experts, top_k):
+    cfg = Config(32, 256, experts, top_k, ffn, attn, expert_alignment=8, payload=payload)
+    world = make_world(cfg)
+    try:
+        for epoch in range(3):
+            batches = [synthetic.exact_batch(cfg, 32, a, epoch) for a in range(attn)]
+            run_and_check(world, cfg, batches)
+    finally:
+        world.close()
+
+
+def test_route_cases_and_host_counts():
+    cfg = Config(16, 512, 8, 2, 2, 2, expert_alignment=128)
+    world = make_world(cfg)
+    n = 16
+    cases = [
+        dict(active=(n, n)),
+        dict(active=(n, n), routing="skew"),
+        dict(active=(n, 0)),
+        dict(active=(n, n), routing="skip"),
+        dict(active=(0, 0)),
+        dict(active=(3, 1)),
+    ]
+    try:
+        for host in (False, True):
+            for epoch, case in enumerate(cases):
+                batches = [
+                    synthetic.exact_batch(cfg, n, a, epoch, active=case["active"][a], routing=case.get("routing", "mixed"))
+                    for a in range(2)
+                ]
+                run_and_check(world, cfg, batches, read_host_counts=host)
+        # fewer tokens than the bucket, and an empty source
+        batches = [synthetic.exact_batch(cfg, 5, 0, 9), synthetic.exact_batch(cfg, 0, 1, 9)]
+        run_and_check(world, cfg, batches, bucket=8)
+    finally:
+        world.close()
+
+
+@pytest.mark.parametrize("payload", ["bf16", "fp8"])
+def test_random_routes_large_hidden(payload):
+    cfg = Config(512, 2048, 32, 8, 2, 2, payload=payload)
+    world = make_world(cfg)
+    try:
+        for seed in range(2):
+            batches = [synthetic.random_batch(cfg, 512 - 37 * a, 100 * seed + a, skip_fraction=0.1) for a in range(2)]
+            run_and_check(world, cfg, batches, exact=True)
+        batches = [synthetic.random_batch(cfg, 300, 7 + a, zipf_s=1.1) for a in range(2)]
+        run_and_check(world, cfg, batches)
+    finally:
+        world.close()
+
+
+def test_strided_scales_and_column_major_output():
+    cfg = Config(16, 512, 8, 2, 2, 2, expert_alignment=4, payload="fp8")
+    world = make_world(cfg, recv_scale_layout="col_major_tma")
+    try:
+        batches = []
+        for a in range(2):
+            x, ids, w, scale = synthetic.exact_batch(cfg, 16, a, 3)
+            wide = torch.full((16, scale.shape[1] * 2), float("nan"))
+            wide[:, ::2] = scale
+            batches.append((x, ids, w, wide))
+        dev = []
+        for x, ids, w, wide in batches:
+            dev.append((x.cuda(), ids.cuda(), w.cuda(), wide.cuda()[:, ::2]))
+        sources = [oracle.SourceBatch(b[0], b[1], b[2], b[3][:, ::2]) for b in batches]
+
+        def expert(i, rec):
+            assert rec.recv_scale.stride(0) == 1 and rec.recv_scale.stride(1) % 4 == 0
+            return oracle.synthetic_expert_rows(cfg, i, rec.recv_x, rec.recv_scale, rec.recv_topk_weights, rec.recv_count_psum)
+
+        outs, received = world.exchange(dev, expert)
+        torch.cuda.synchronize()
+        for a, out in enumerate(outs):
+            assert torch.equal(out.cpu().float(), oracle.expected_combine(cfg, sources[a]).float())
+        for f, rec in enumerate(received):
+            exp = oracle.expected_receive(cfg, f, sources, rows=rec.recv_x.shape[0])
+            assert torch.equal(rec.recv_scale.cpu()[exp.valid], exp.recv_scale[exp.valid])
+    finally:
+        world.close()
+
+
+@pytest.mark.parametrize("kind", ["outside", "negative", "wide", "duplicate"])
+def test_illegal_route_is_reported_not_trapped(kind):
+    cfg = Config(16, 256, 8, 2, 2, 2, expert_alignment=4)
+    world = make_world(cfg)
+    try:
+        batches = [list(synthetic.exact_batch(cfg, 16, a, 1)) for a in range(2)]
+        ids = batches[0][1]
+        if kind == "duplicate":
+            ids[3, 1] = ids[3, 0]
+        else:
+            ids[3, 0] = {"outside": cfg.num_experts, "negative": -2, "wide": 1 << 32}[kind]
+        dev = [to_dev(b) for b in batches]
+
+        def expert(i, rec):
+            return oracle.synthetic_expert_rows(cfg, i, rec.recv_x, rec.recv_scale, rec.recv_topk_weights, rec.recv_count_psum)
+
+        outs, _ = world.exchange(dev, expert)
+        torch.cuda.synchronize()
+        # The offending token collects as zeros, every other token is untouched.
+        expect = oracle.expected_combine(cfg, oracle.SourceBatch(*batches[0]))
+        assert torch.equal(outs[0].cpu().float(), expect.float())
+        assert not outs[0][3].any()
+        with pytest.raises(AfdepRouteError, match="illegal route"):
+            world.attention[0].check()
+        world.attention[0].check()    # reported once, then cleared
+        # the context is alive and the next exchange is clean
+        clean = [synthetic.exact_batch(cfg, 16, a, 2) for a in range(2)]
+        run_and_check(world, cfg, clean)
+    finally:
+        world.close()
+
+
+def test_bounded_wait_reports_timeout_instead_of_hanging():
+    """An FFN rank that receives without any dispatch gives up after its budget."""
+    from afdep_b200 import AfdepTimeoutError
+
+    cfg = Config(8, 256, 8, 2, 1, 1, expert_alignment=1)
+    world = make_world(cfg)
+    world.close()
+    from afdep_b200.parallel.loopback import LoopbackWorld
+
+    world = LoopbackWorld(cfg, gpu_timeout_s=0.05)
+    try:
+        rec = world.ffn[0].worker_receive(bucket=8)
+        torch.cuda.synchronize()          # returns: the wait is bounded
+        with pytest.raises(AfdepTimeoutError, match="counts"):
+            world.ffn[0].check()
+        assert rec.recv_x.shape[0] == cfg.receive_rows(8)
+        # the CUDA context still works
+        assert float(torch.ones(4, device="cuda").sum()) == 4.0
+    finally:
+        for b in world.buffers:
+            b.transport._pending = None
+        world.close()
+
+
+def test_cuda_graph_replay_with_changed_inputs():
+    cfg = Config(16, 512, 8, 2, 2, 2, expert_alignment=4)
+    world = make_world(cfg)
+    try:
+        n, steps = 16, 3
+        first = [to_dev(synthetic.exact_batch(cfg, n, a, 0)) for a in range(2)]
+        static = [[t.clone() if t is not None else None for t in b] for b in first]
+
+        def expert(i, rec):
+            return oracle.synthetic_expert_rows(cfg, i, rec.recv_x, rec.recv_scale, rec.recv_topk_weights, rec.recv_count_psum)
+
+        stream = torch.cuda.Stream()
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            for _ in range(2):
+                world.exchange(static, expert)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            captured = [world.exchange(static, expert)[0] for _ in range(steps)]
+        for epoch in range(1, 5):
+            routing = "skip" if epoch == 3 else "mixed"
+            new = [synthetic.exact_batch(cfg, n, a, epoch, active=n - 3 * a, routing=routing) for a in range(2)]
+            for s, b in zip(static, new):
+                for dst, src in zip(s, b):
+                    if dst is not None:
+                        dst.copy_(src)
+            graph.replay()
+            torch.cuda.synchronize()
+            for a in range(2):
+                expect = oracle.expected_combine(cfg, oracle.SourceBatch(*new[a])).float()
+                for outs in captured:
+                    assert torch.equal(outs[a].cpu().float(), expect)
+        for b in world.buffers:
+            b.check()
+    finally:
+        world.close()
