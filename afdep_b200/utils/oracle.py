@@ -184,13 +184,14 @@ def expected_combine(config: Config, src: SourceBatch, expert_fn=None, stages: s
             continue
         ex = e.clamp(min=0)
         if expert_fn is None:
-            y = xf * (ex + 1).float()[:, None]
+            # same operation order as synthetic_expert_rows: (x * weight) * (e + 1)
+            y = xf * w[:, k][:, None] * (ex + 1).float()[:, None]
         else:
             y = torch.zeros_like(xf)
             for ee in torch.unique(ex[sel]).tolist():
                 m = sel & (ex == ee)
-                y[m] = expert_fn(int(ee), xf[m])
-        row = (y * w[:, k][:, None]).to(torch.bfloat16).float()   # the caller replies in BF16
+                y[m] = expert_fn(int(ee), xf[m]) * w[m, k][:, None]
+        row = y.to(torch.bfloat16).float()   # the caller replies in BF16
         row = torch.where(sel[:, None], row, torch.zeros_like(row))
         if stages == "single_stage":
             out += row

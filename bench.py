@@ -76,11 +76,12 @@ class ClockSampler:
     def start(self) -> None:
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50", "-i", str(self.index)],
                 stdout=subprocess.PIPE,
                 stderr=subprocess.DEVNULL,
                 text=True,
             )
+            self.first = self.proc.stdout.readline()   # blocks until the sampler is really running
         except OSError:
             self.proc = None
 
@@ -95,7 +96,7 @@ class ClockSampler:
             out, _ = self.proc.communicate()
         sm, mx, reasons = [], [], set()
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for line in out.splitlines():
+        for line in [getattr(self, "first", "")] + out.splitlines():
             f = [s.strip() for s in line.split(",")]
             if len(f) < 9:
                 continue

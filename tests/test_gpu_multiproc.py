@@ -1,0 +1,150 @@
+"""The CUDA transport across real GPUs: one process per GPU, heaps mapped over NVLink.
+
+Children rendezvous over Gloo on 127.0.0.1, build a native ``Buffer`` each, run exchanges
+through the role API and compare with the oracle.  Failure detection is exercised from the
+host side only: an FFN rank whose host skips its reply makes the attention rank's bounded
+wait run out, which surfaces as ``AfdepTimeoutError`` while the CUDA context stays usable.
+"""
+
+import os
+
+import pytest
+import torch
+
+from afdep_b200 import AfdepTimeoutError, Buffer, Config
+from afdep_b200.utils import oracle, synthetic
+from tests._dist import run_ranks
+
+
+def _to_dev(batch):
+    return tuple(None if t is None else t.cuda() for t in batch)
+
+
+def _exchange_once(buf, cfg, batches, *, tokens, read_host_counts=False):
+    sources = [oracle.SourceBatch(*b) for b in batches]
+    if buf.role == "attention":
+        x, ids, w, scale = _to_dev(batches[buf.role_rank])
+        buf.source_dispatch(x, ids, w, scale, bucket=cfg.capacity_tokens_per_rank, read_host_counts=read_host_counts)
+        out = buf.source_collect()
+        torch.cuda.synchronize()
+        buf.check()
+        expect = oracle.expected_combine(cfg, sources[buf.role_rank])
+        assert torch.equal(out.cpu().float(), expect.float()), f"combine differs on attention rank {buf.role_rank}"
+    else:
+        rec = buf.worker_receive(bucket=cfg.capacity_tokens_per_rank, read_host_counts=read_host_counts)
+        rows = oracle.synthetic_expert_rows(cfg, buf.role_rank, rec.recv_x, rec.recv_scale, rec.recv_topk_weights, rec.recv_count_psum)
+        buf.worker_reply(rows, rec.receipt)
+        torch.cuda.synchronize()
+        buf.check()
+        exp = oracle.expected_receive(cfg, buf.role_rank, sources, rows=rec.recv_x.shape[0])
+        assert torch.equal(rec.recv_count_psum.cpu().long(), exp.layout.ends)
+        v = exp.valid
+        assert torch.equal(rec.recv_x.cpu()[v].float(), exp.recv_x[v].float())
+        assert torch.equal(rec.recv_topk_weights.cpu()[v], exp.recv_weights[v])
+        if read_host_counts:
+            assert rec.recv_counts_host == exp.layout.aligned_counts
+
+
+def _roundtrip(rank, world, ffn, payload, hidden, tokens, experts, top_k):
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    attn = world - ffn
+    cfg = Config(tokens, hidden, experts, top_k, ffn, attn, expert_alignment=16, payload=payload, gpu_timeout_s=10)
+    buf = Buffer(group=dist.group.WORLD, config=cfg)
+    assert buf.transport._transport.heap_mode in ("vmm", "ipc")
+    for epoch in range(3):
+        batches = [synthetic.random_batch(cfg, tokens - 11 * a, seed=17 * epoch + a, skip_fraction=0.05) for a in range(attn)]
+        _exchange_once(buf, cfg, batches, tokens=tokens, read_host_counts=(epoch == 2))
+    # graph replay of complete pairs with inputs changed in place
+    static = [_to_dev(synthetic.random_batch(cfg, tokens, seed=900 + a)) for a in range(attn)]
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+
+    def pair():
+        if buf.role == "attention":
+            x, ids, w, scale = static[buf.role_rank]
+            buf.source_dispatch(x, ids, w, scale, bucket=tokens)
+            return buf.source_collect()
+        rec = buf.worker_receive(bucket=tokens)
+        rows = oracle.synthetic_expert_rows(cfg, buf.role_rank, rec.recv_x, rec.recv_scale, rec.recv_topk_weights, rec.recv_count_psum)
+        buf.worker_reply(rows, rec.receipt)
+        return None
+
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            pair()
+    torch.cuda.synchronize()
+    dist.barrier()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        outs = [pair() for _ in range(3)]
+    for epoch in range(3):
+        new = [synthetic.random_batch(cfg, tokens, seed=300 + 10 * epoch + a, skip_fraction=0.2 * epoch) for a in range(attn)]
+        if buf.role == "attention":
+            for dst, src in zip(static[buf.role_rank], new[buf.role_rank]):
+                if dst is not None:
+                    dst.copy_(src)
+        if buf.role == "ffn" and buf.role_rank == 0 and epoch == 1:
+            torch.cuda._sleep(2_000_000)          # a late FFN peer
+        graph.replay()
+        torch.cuda.synchronize()
+        buf.check()
+        if buf.role == "attention":
+            expect = oracle.expected_combine(cfg, oracle.SourceBatch(*new[buf.role_rank])).float()
+            for out in outs:
+                assert torch.equal(out.cpu().float(), expect)
+        dist.barrier()
+    del graph
+    buf.close()
+
+
+@pytest.mark.multigpu(2)
+@pytest.mark.parametrize("payload", ["bf16", "fp8"])
+def test_two_gpus_one_attention_one_ffn(payload):
+    run_ranks(_roundtrip, 2, 1, payload, 1024, 256, 16, 4, timeout=600)
+
+
+@pytest.mark.multigpu(4)
+@pytest.mark.parametrize("payload", ["bf16", "fp8"])
+def test_four_gpus_two_by_two(payload):
+    run_ranks(_roundtrip, 4, 2, payload, 2048, 512, 32, 8, timeout=600)
+
+
+@pytest.mark.multigpu(8)
+def test_eight_gpus_six_attention_two_ffn():
+    run_ranks(_roundtrip, 8, 2, "bf16", 2048, 128, 64, 8, timeout=900)
+
+
+def _withheld_reply(rank, world):
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    cfg = Config(64, 512, 8, 2, 1, 1, expert_alignment=8)
+    buf = Buffer(group=dist.group.WORLD, config=cfg, gpu_timeout_s=0.5)
+    batch = synthetic.random_batch(cfg, 64, seed=5)
+    # one good exchange first
+    _exchange_once(buf, cfg, [batch], tokens=64)
+    dist.barrier()
+    if buf.role == "attention":
+        x, ids, w, scale = _to_dev(batch)
+        buf.source_dispatch(x, ids, w, scale, bucket=64)
+        out = buf.source_collect()        # the peer's host never replies
+        torch.cuda.synchronize()          # returns after the bounded wait
+        with pytest.raises(AfdepTimeoutError, match="reply"):
+            buf.check()
+        assert float(torch.ones(8, device="cuda").sum()) == 8.0   # the context is intact
+        assert out.shape == (64, 512)
+    else:
+        rec = buf.worker_receive(bucket=64)
+        torch.cuda.synchronize()
+        assert int(rec.recv_count_psum[-1]) > 0
+        buf.transport._pending = None      # the failure being simulated: this host gives up here
+    dist.barrier()                         # ranks learn of the failure on the host, between steps
+    buf.close()
+
+
+@pytest.mark.multigpu(2)
+def test_withheld_reply_times_out_cleanly():
+    run_ranks(_withheld_reply, 2, timeout=300)
