@@ -26,7 +26,7 @@ struct WaitCtx {
 
 __device__ __forceinline__ void report(const WaitCtx& w, int code, int peer, unsigned epoch, long long expected,
                                        long long observed, int d0 = 0, int d1 = 0) {
-    if (atomicCAS(&w.poison[kClaim], 0, code) == 0) {
+    if (atomicCAS(&w.poison[kClaim], 0, code) == 0 && w.status != nullptr) {
         volatile Status* s = w.status;
         s->kernel = w.kernel;
         s->rank = w.rank;
@@ -55,6 +55,12 @@ __device__ __forceinline__ bool spin_until(const WaitCtx& w, Ready ready) {
             if (clock64() - t0 > w.budget) return false;
         }
     }
+}
+
+// One thread per CTA records a time stamp when tracing is on.
+__device__ __forceinline__ void trace_stamp(unsigned long long* trace, int kernel, int stamp) {
+    if (trace != nullptr && threadIdx.x == 0 && blockIdx.x < 320)
+        trace[((size_t)kernel * 320 + blockIdx.x) * 4 + stamp] = ptx::globaltimer_ns();
 }
 
 __device__ __forceinline__ void poison(const WaitCtx& w) { atomicExch(w.poison + kPoison, 1); }

@@ -45,6 +45,7 @@ collect_kernel(const RankCtx c, const AttnWs ws, unsigned char* __restrict__ out
     }
     __syncwarp();
 
+    trace_stamp(c.trace, kTraceCollect, 0);
     const int nvec = g.hidden / 8;
     unsigned it = 0;
     for (int t = cta * NW + warp; t < T; t += G * NW) {
@@ -117,6 +118,7 @@ collect_kernel(const RankCtx c, const AttnWs ws, unsigned char* __restrict__ out
     }
 
     __syncthreads();
+    trace_stamp(c.trace, kTraceCollect, 2);
     if (tid == 0) {
         __threadfence();
         if (atomicAdd(&ws.ticket[1], 1u) == (unsigned)(G - 1)) {

@@ -12,175 +12,57 @@
 //
 // Phase 2 (push) — one warp per token: a bulk async copy brings the row into shared memory
 // once, lanes append scales/routes/weights, and one bulk store per destination FFN rank
-// writes the finished record straight into that rank's staging slot over NVLink.  After a
-// store group has completed, the warp releases one 4-byte arrival flag per record, so the
-// receiver can start on a record as soon as it has landed.
+// writes the finished record straight into that rank's staging slot over NVLink.  Once a
+// store group has completed, the data warp hands the token to the CTA's flag warp, which
+// issues the system-scope fence and the 4-byte arrival flag per record; the receiver can
+// start on a record as soon as it has landed, and the (slow) fence never stalls a data warp.
 //
 // Replaces, for the AFD case, the reference's dispatch_impl (notify + dispatch warps,
 // deep_ep/include/deep_ep/impls/dispatch.cuh:18-433), its deterministic prologue
 // (dispatch_deterministic_prologue.cuh) and the stand-alone route guard (afdep_roles.cuh:11-33)
 // without the two grid-wide GPU barriers those need, and never traps on a bad route.
 #include "afdep/kernels.h"
+#include "afdep/route_layout.cuh"
 #include "afdep/status.cuh"
 
 namespace afdep {
 
 namespace {
 
-constexpr int kNB = 2;            // record buffers per warp
 constexpr int kBarBytes = 1024;   // mbarrier area at the start of dynamic shared memory
 constexpr int kMaxWarps = 16;
 constexpr int kMaxCtas = 160;
 
-__device__ __forceinline__ int align_up_dev(int v, int a) { return (v + a - 1) / a * a; }
-
+// NB record buffers per warp form a ring: while token i is being stored, token i+1 is
+// already loading, and the arrival flags of token i-(NB-2) are released once its store group
+// has completed.  NB = 2 degenerates to load -> store -> wait -> flag.
+template <int NB>
 __global__ void __launch_bounds__(kMaxWarps * 32, 1)
 dispatch_kernel(const RankCtx c, const AttnWs ws, const DispatchArgs a) {
+    constexpr int L = NB - 2;     // how many tokens the flag release lags behind the stores
     extern __shared__ __align__(128) unsigned char smem[];
     const Geometry& g = c.g;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, NW = blockDim.x >> 5;
     const int G = gridDim.x, cta = blockIdx.x;
     const int F = g.ffn, K = g.top_k, E = g.num_experts, EL = g.experts_local, C = g.capacity;
-    const int ncols = F + E;
     const int ai = c.role_rank;
     const unsigned ep = ptx::ld_acquire_gpu(&ws.epoch[0]) + 1u;
     const WaitCtx wc{c.status, c.poison, c.budget, c.rank, /*kernel=*/1};
+    (void)L;
+    trace_stamp(c.trace, kTraceDispatch, 0);
 
     const int T = a.T;
     const int chunk = (T + G - 1) / G;
     const int t0 = min(T, cta * chunk), t1 = min(T, t0 + chunk);
-    const int n = t1 - t0;
-    const int sub = (n + NW - 1) / NW;
-    const int w0 = min(t1, t0 + warp * sub), w1 = min(t1, w0 + sub);
 
     // ------------------------------------------------------------------ phase 1: layout
-    int* wh = reinterpret_cast<int*>(smem + kBarBytes);   // [NW][ncols] per-warp histograms
-    int* tot = wh + NW * ncols;                            // [ncols] CTA totals
-    int* lb = tot + ncols;                                 // [ncols] sum over earlier CTAs
-    for (int i = tid; i < (NW + 2) * ncols; i += blockDim.x) wh[i] = 0;
-    for (int i = tid; i < n * F; i += blockDim.x) ws.tok_slot[(size_t)t0 * F + i] = -1;
-    __syncthreads();
-
-    {
-        const int tpb = 32 / K;                 // tokens handled per warp step
-        const int tl = lane / K, k = lane - tl * K;
-        const bool lane_on = tl < tpb;
-        const unsigned kmask = (K == 32) ? 0xffffffffu : ((1u << K) - 1u);
-        const unsigned grp = lane_on ? (kmask << (tl * K)) : 0u;
-        const unsigned lt = ptx::lanemask_lt();
-        int* my = wh + warp * ncols;
-        constexpr int U = 4;                    // steps whose ids are fetched together
-        for (int tb0 = w0; tb0 < w1; tb0 += tpb * U) {
-            long long idv[U];
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int t = tb0 + u * tpb + tl;
-                idv[u] = (lane_on && t < w1) ? a.ids[(size_t)t * K + k] : -1ll;
-            }
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int tb = tb0 + u * tpb;
-                if (tb >= w1) break;            // warp-uniform
-                const int t = tb + tl;
-                const bool in = lane_on && t < w1;
-                const long long id = idv[u];
-                // Range check at full width, before narrowing to int.
-                bool bad = in && (id < -1ll || id >= (long long)E);
-                int e = (in && !bad && id >= 0) ? (int)id : -1;
-                int key = (e >= 0) ? (tl * kMaxExperts + e) : -(lane + 1);
-                unsigned peers = __match_any_sync(ptx::kFullMask, key);
-                if (e >= 0 && __popc(peers) > 1) bad = true;      // expert repeated in a token
-                const unsigned badmask = __ballot_sync(ptx::kFullMask, bad);
-                if (bad) {
-                    report(wc, kBadRoute, -1, ep, t, id, k, 0);
-                    atomicAdd(&c.poison[kBadRoutes], 1);
-                }
-                if (badmask & grp) e = -1;      // an illegal token publishes nothing
-
-                // rank of this choice among the warp's earlier choices of the same expert
-                key = (e >= 0) ? e : -(lane + 1);
-                peers = __match_any_sync(ptx::kFullMask, key);
-                const int rank_e = __popc(peers & lt);
-                int pos = -1;
-                if (e >= 0) pos = my[F + e] + rank_e;
-                __syncwarp();
-                if (e >= 0 && rank_e == 0) my[F + e] += __popc(peers);
-
-                // one record per (token, FFN rank): the lowest lane of the pair claims a slot
-                const int f = (e >= 0) ? e / EL : -1;
-                key = (e >= 0) ? (tl * 64 + f) : -(lane + 1);
-                const unsigned ptf = __match_any_sync(ptx::kFullMask, key);
-                const bool lead = (e >= 0) && ((ptf & lt) == 0u);
-                key = lead ? f : -(lane + 1);
-                const unsigned pf = __match_any_sync(ptx::kFullMask, key);
-                const int rank_f = __popc(pf & lt);
-                int slot = -1;
-                if (lead) slot = my[f] + rank_f;
-                __syncwarp();
-                if (lead && rank_f == 0) my[f] += __popc(pf);
-                __syncwarp();
-
-                if (in) {
-                    ws.route_e[(size_t)t * K + k] = e;
-                    ws.route_pos[(size_t)t * K + k] = pos;
-                }
-                if (lead) ws.tok_slot[(size_t)t * F + f] = slot;
-            }
-        }
-    }
-    __syncthreads();
-
-    // exclusive scan over the CTA's warps, publish the CTA aggregate
-    for (int col = tid; col < ncols; col += blockDim.x) {
-        int run = 0;
-        for (int w = 0; w < NW; ++w) {
-            const int v = wh[w * ncols + col];
-            wh[w * ncols + col] = run;
-            run += v;
-        }
-        tot[col] = run;
-        ptx::st_relaxed_gpu_u64(&ws.agg[(size_t)cta * ncols + col],
-                                ((unsigned long long)ep << 32) | (unsigned)run);
-    }
-
-    // decoupled look-back: sum the aggregates of all earlier CTAs
-    {
-        constexpr int U = 8;
-        const int total = cta * ncols;
-        bool ok = true;
-        for (int base = tid; base < total && ok; base += blockDim.x * U) {
-            unsigned long long v[U];
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int idx = base + u * blockDim.x;
-                v[u] = (idx < total) ? ptx::ld_relaxed_gpu_u64(&ws.agg[idx]) : 0ull;
-            }
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-                const int idx = base + u * blockDim.x;
-                if (idx >= total) break;
-                if ((unsigned)(v[u] >> 32) != ep) {
-                    unsigned long long vv = v[u];
-                    ok = spin_until(wc, [&] {
-                        vv = ptx::ld_relaxed_gpu_u64(&ws.agg[idx]);
-                        return (unsigned)(vv >> 32) == ep;
-                    });
-                    if (!ok) {
-                        report(wc, kTimeoutLookback, idx / ncols, ep, ep, (long long)(vv >> 32), cta, 0);
-                        poison(wc);
-                        break;
-                    }
-                    v[u] = vv;
-                }
-                const int cnt = (int)(unsigned)v[u];
-                if (cnt) atomicAdd(&lb[idx % ncols], cnt);
-            }
-        }
-    }
-    __syncthreads();
+    int *tot = nullptr, *lb = nullptr;
+    const RouteLayoutOut lo{ws.route_e, ws.route_pos, ws.tok_slot};
+    bool alive = route_layout_phase(a.ids, T, K, E, EL, F, ep, ws.agg, lo, reinterpret_cast<int*>(smem + kBarBytes), wc,
+                                    &tot, &lb);
 
     // The last CTA now holds this source's totals: push them to the FFN ranks.
-    if (cta == G - 1) {
+    if (cta == G - 1 && alive) {
         const int cs = cnt_stride(g);
         for (int idx = tid; idx < F * (EL + 1); idx += blockDim.x) {
             const int f = idx / (EL + 1), el = idx - f * (EL + 1);
@@ -194,116 +76,140 @@ dispatch_kernel(const RankCtx c, const AttnWs ws, const DispatchArgs a) {
             ptx::st_relaxed_sys(reinterpret_cast<uint32_t*>(c.peer[tid] + g.f_cnt_flag) + ai * 32, ep);
         }
     }
-
-    // fix-up: warp-local ranks -> global pos / slot
-    {
-        const int* my = wh + warp * ncols;
-        const int cntk = (w1 - w0) * K;
-        for (int i = lane; i < cntk; i += 32) {
-            const size_t idx = (size_t)w0 * K + i;
-            const int e = ws.route_e[idx];
-            if (e >= 0) ws.route_pos[idx] += my[F + e] + lb[F + e];
-        }
-        const int cntf = (w1 - w0) * F;
-        for (int i = lane; i < cntf; i += 32) {
-            const size_t idx = (size_t)w0 * F + i;
-            const int f = i % F;
-            const int s = ws.tok_slot[idx];
-            if (s >= 0) ws.tok_slot[idx] = s + my[f] + lb[f];
-        }
-    }
     // Shared memory changes hands from generic-proxy scratch to bulk-copy buffers.
     ptx::fence_proxy_async_smem();
     __syncthreads();
+    trace_stamp(c.trace, kTraceDispatch, 1);
 
     // ------------------------------------------------------------------ phase 2: push
+    // Warps [0, ND) move data; the last warp releases arrival flags.
+    const int ND = NW - 1;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
-    unsigned char* bufs = smem + kBarBytes + (size_t)warp * kNB * g.rec_bytes;
-    if (lane == 0) {
-        for (int b = 0; b < kNB; ++b) ptx::mbar_init(&bars[warp * kNB + b], 1);
+    int* done_cnt = reinterpret_cast<int*>(smem + kBarBytes - 128);   // [ND] tokens completed per data warp
+    unsigned char* bufs = smem + kBarBytes + (size_t)warp * NB * g.rec_bytes;
+    if (warp < ND && lane == 0) {
+        for (int b = 0; b < NB; ++b) ptx::mbar_init(&bars[warp * NB + b], 1);
         ptx::fence_mbar_init();
     }
-    __syncwarp();
+    if (tid < 32) done_cnt[tid] = 0;
+    __syncthreads();
 
     const unsigned char* xb = static_cast<const unsigned char*>(a.x);
     const int sg = g.fp8 ? g.scale_groups : 0;
-    int it = 0;
-    int pend_slot = -1;
-    unsigned pend_mask = 0;
-    bool alive = true;
-    for (int t = t0 + warp; t < t1 && alive; t += NW) {
-        const int slot = (lane < F) ? ws.tok_slot[(size_t)t * F + lane] : -1;
-        const unsigned mask = __ballot_sync(ptx::kFullMask, slot >= 0);
-        if (mask == 0) continue;
-        const int b = it % kNB;
-        const unsigned parity = (it / kNB) & 1u;
-        unsigned char* buf = bufs + (size_t)b * g.rec_bytes;
-        uint64_t* bar = &bars[warp * kNB + b];
-        if (lane == 0) {
-            if (it >= kNB) ptx::bulk_wait_read<kNB - 1>();   // buffer's previous stores have read it
-            ptx::mbar_expect_tx(bar, g.payload_bytes);
-            ptx::bulk_load(buf, xb + (size_t)t * g.payload_bytes, g.payload_bytes, bar);
-        }
-        __syncwarp();
-        int* meta = reinterpret_cast<int*>(buf + g.meta_off);
-        if (lane < K) {
-            meta[lane] = ws.route_e[(size_t)t * K + lane];
-            meta[K + lane] = ws.route_pos[(size_t)t * K + lane];
-            reinterpret_cast<float*>(meta)[2 * K + lane] = a.weights[(size_t)t * K + lane];
-        }
-        if (lane == 0) meta[3 * K] = t;
-        for (int gi = lane; gi < sg; gi += 32)
-            reinterpret_cast<float*>(buf + g.payload_bytes)[gi] = a.x_scale[(size_t)t * a.ss0 + (size_t)gi * a.ss1];
-        ptx::fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-            // A local bulk load always completes; the bound only guards against a broken build.
-            alive = spin_until(wc, [&] { return ptx::mbar_try_wait(bar, parity); });
-        }
-        alive = __shfl_sync(ptx::kFullMask, alive, 0);
-        if (!alive) break;
-        for (unsigned m = mask; m; m &= m - 1) {
-            const int f = __ffs(m) - 1;
-            const int s = __shfl_sync(ptx::kFullMask, slot, f);
+    auto tokens_of = [&](int w) { return (alive && t0 + w < t1) ? (t1 - (t0 + w) + ND - 1) / ND : 0; };
+
+    if (warp < ND) {
+        const int first = t0 + warp;
+        const int n_w = tokens_of(warp);
+        unsigned phase_bits = 0;      // lane 0: parity of each buffer's mbarrier
+
+        // A(i): start loading token i into its ring buffer and append its metadata.
+        auto stage = [&](int i, int& slot, unsigned& mask) {
+            const int t = first + i * ND;
+            slot = (lane < F) ? ws.tok_slot[(size_t)t * F + lane] : -1;
+            mask = __ballot_sync(ptx::kFullMask, slot >= 0);
+            if (mask == 0) return;
+            unsigned char* buf = bufs + (size_t)(i % NB) * g.rec_bytes;
             if (lane == 0) {
-                const bool inb = !c.bounds_check || (s >= 0 && s < C);
-                if (inb)
-                    ptx::bulk_store(c.peer[f] + g.f_stage + ((size_t)ai * C + s) * g.rec_bytes, buf, g.rec_bytes);
-                else
-                    report(wc, kBadIndex, f, ep, C, s, t, 1);
+                uint64_t* bar = &bars[warp * NB + (i % NB)];
+                ptx::mbar_expect_tx(bar, g.payload_bytes);
+                ptx::bulk_load(buf, xb + (size_t)t * g.payload_bytes, g.payload_bytes, bar);
             }
-        }
-        if (lane == 0) ptx::bulk_commit();
-        // release the arrival flags of the previous token, whose stores have now completed
-        if (pend_mask) {
+            int* meta = reinterpret_cast<int*>(buf + g.meta_off);
+            if (lane < K) {
+                meta[lane] = ws.route_e[(size_t)t * K + lane];
+                meta[K + lane] = ws.route_pos[(size_t)t * K + lane];
+                reinterpret_cast<float*>(meta)[2 * K + lane] = a.weights[(size_t)t * K + lane];
+            }
+            if (lane == 0) meta[3 * K] = t;
+            for (int gi = lane; gi < sg; gi += 32)
+                reinterpret_cast<float*>(buf + g.payload_bytes)[gi] = a.x_scale[(size_t)t * a.ss0 + (size_t)gi * a.ss1];
+            ptx::fence_proxy_async_smem();
+        };
+
+        int slot_c = -1, slot_n = -1;
+        unsigned mask_c = 0, mask_n = 0;
+        bool ok = true;
+        if (n_w > 0) stage(0, slot_c, mask_c);
+        for (int i = 0; i < n_w; ++i) {
+            // Buffer (i+1) % NB last held token i+1-NB, whose stores completed at step i-1.
+            if (i + 1 < n_w) stage(i + 1, slot_n, mask_n);
+            __syncwarp();
+            if (mask_c) {
+                const int b = i % NB;
+                unsigned char* buf = bufs + (size_t)b * g.rec_bytes;
+                if (lane == 0) {
+                    uint64_t* bar = &bars[warp * NB + b];
+                    const unsigned parity = (phase_bits >> b) & 1u;
+                    // A local bulk load always completes; the bound only guards against a broken build.
+                    ok = spin_until(wc, [&] { return ptx::mbar_try_wait(bar, parity); });
+                    phase_bits ^= 1u << b;
+                }
+                ok = __shfl_sync(ptx::kFullMask, ok, 0);
+                if (!ok) break;
+                const int t = first + i * ND;
+                for (unsigned m = mask_c; m; m &= m - 1) {
+                    const int f = __ffs(m) - 1;
+                    const int s = __shfl_sync(ptx::kFullMask, slot_c, f);
+                    if (lane == 0) {
+                        const bool inb = !c.bounds_check || (s >= 0 && s < C);
+                        if (inb)
+                            ptx::bulk_store(c.peer[f] + g.f_stage + ((size_t)ai * C + s) * g.rec_bytes, buf, g.rec_bytes);
+                        else
+                            report(wc, kBadIndex, f, ep, C, s, t, 1);
+                    }
+                }
+            }
             if (lane == 0) {
-                ptx::bulk_wait<kNB - 1>();
+                ptx::bulk_commit();            // one group per token, possibly empty
+                if (i >= L) {
+                    ptx::bulk_wait<L>();       // token i-L has fully landed at its destinations
+                    ptx::st_release_cta_shared(&done_cnt[warp], i - L + 1);
+                }
+            }
+            slot_c = slot_n;
+            mask_c = mask_n;
+        }
+        if (lane == 0) {
+            ptx::bulk_wait<0>();
+            ptx::st_release_cta_shared(&done_cnt[warp], ok ? n_w : -1);
+        }
+    } else {
+        // Flag warp: lane w follows data warp w.
+        const int mine = (lane < ND) ? tokens_of(lane) : 0;
+        int flagged = 0;
+        bool aborted = false;
+        const long long t_begin = clock64();
+        unsigned idle = 0;
+        while (true) {
+            int d = (lane < ND && !aborted) ? ptx::ld_acquire_cta_shared(&done_cnt[lane]) : flagged;
+            if (d < 0) {
+                aborted = true;
+                d = flagged;
+            }
+            if (d > flagged) {
                 ptx::fence_acq_rel_sys();
+                for (int j = flagged; j < d; ++j) {
+                    const int t = t0 + lane + j * ND;
+                    for (int f = 0; f < F; ++f) {
+                        const int s = ws.tok_slot[(size_t)t * F + f];
+                        if (s >= 0 && s < C)
+                            ptx::st_relaxed_sys(reinterpret_cast<uint32_t*>(c.peer[f] + g.f_slot_flag) + (size_t)ai * C + s, ep);
+                    }
+                }
+                flagged = d;
+                idle = 0;
             }
-            for (unsigned m = pend_mask; m; m &= m - 1) {
-                const int f = __ffs(m) - 1;
-                const int s = __shfl_sync(ptx::kFullMask, pend_slot, f);
-                if (lane == 0 && s >= 0 && s < C)
-                    ptx::st_relaxed_sys(reinterpret_cast<uint32_t*>(c.peer[f] + g.f_slot_flag) + (size_t)ai * C + s, ep);
-            }
-        }
-        pend_mask = mask;
-        pend_slot = slot;
-        ++it;
-    }
-    if (lane == 0) ptx::bulk_wait<0>();
-    if (pend_mask && alive) {
-        if (lane == 0) ptx::fence_acq_rel_sys();
-        for (unsigned m = pend_mask; m; m &= m - 1) {
-            const int f = __ffs(m) - 1;
-            const int s = __shfl_sync(ptx::kFullMask, pend_slot, f);
-            if (lane == 0 && s >= 0 && s < C)
-                ptx::st_relaxed_sys(reinterpret_cast<uint32_t*>(c.peer[f] + g.f_slot_flag) + (size_t)ai * C + s, ep);
+            const bool fin = lane >= ND || aborted || flagged >= mine;
+            if (__all_sync(ptx::kFullMask, fin)) break;
+            if (++idle > 1) __nanosleep(64);
+            if ((idle & 255u) == 0 && (poisoned(wc) || clock64() - t_begin > 4 * c.budget)) break;
         }
     }
 
     // The last CTA to get here closes the exchange on this side.
     __syncthreads();
+    trace_stamp(c.trace, kTraceDispatch, 2);
     if (tid == 0) {
         __threadfence();
         if (atomicAdd(&ws.ticket[0], 1u) == (unsigned)(G - 1)) {
@@ -314,6 +220,17 @@ dispatch_kernel(const RankCtx c, const AttnWs ws, const DispatchArgs a) {
     }
 }
 
+// Opt-in shared memory left for the dynamic part, set by configure_dispatch.
+int g_dyn_smem = 227 * 1024 - 256;
+
+int pick_buffers(const Geometry& g) {
+    // Deepest ring that still leaves enough warps per CTA to hide the layout phase.
+    const int avail = g_dyn_smem - kBarBytes;
+    if (avail / (4 * g.rec_bytes) >= 6) return 4;
+    if (avail / (3 * g.rec_bytes) >= 3) return 3;
+    return 2;
+}
+
 }  // namespace
 
 int max_dispatch_ctas() { return kMaxCtas; }
@@ -321,33 +238,49 @@ int max_dispatch_ctas() { return kMaxCtas; }
 LaunchShape dispatch_shape(const Geometry& g, int tokens, int num_sms, int max_smem) {
     LaunchShape s{};
     const int ncols = g.ffn + g.num_experts;
-    int warps = (max_smem - kBarBytes) / (kNB * g.rec_bytes);
-    if (warps > kMaxWarps) warps = kMaxWarps;
-    if (warps < 1) warps = 1;
+    (void)max_smem;
+    const int max_dyn = g_dyn_smem;
+    const int nb = pick_buffers(g);
+    int data_warps = (max_dyn - kBarBytes) / (nb * g.rec_bytes);
+    if (data_warps > kMaxWarps - 1) data_warps = kMaxWarps - 1;
+    if (data_warps < 1) data_warps = 1;
+    int warps = data_warps + 1;          // plus the flag warp
     // Phase 1 scratch must fit too.
-    while (warps > 1 && kBarBytes + (warps + 2) * ncols * 4 > max_smem) --warps;
+    while (warps > 2 && kBarBytes + route_layout_scratch_ints(warps, ncols) * 4 > max_dyn) --warps;
     int ctas = num_sms < kMaxCtas ? num_sms : kMaxCtas;
     // No point in more CTAs than there are warp-sized groups of tokens.
-    int want = (tokens + warps - 1) / warps;
+    int want = (tokens + warps - 2) / (warps - 1);
     if (want < 1) want = 1;
     if (ctas > want) ctas = want;
     if (ctas < 1) ctas = 1;
     s.ctas = ctas;
     s.warps = warps;
-    int p1 = kBarBytes + (warps + 2) * ncols * 4;
-    int p2 = kBarBytes + warps * kNB * g.rec_bytes;
+    const int p1 = kBarBytes + route_layout_scratch_ints(warps, ncols) * 4;
+    const int p2 = kBarBytes + (warps - 1) * nb * g.rec_bytes;
     s.smem_bytes = p1 > p2 ? p1 : p2;
     return s;
 }
 
 cudaError_t launch_dispatch(const RankCtx& c, const AttnWs& ws, const DispatchArgs& a, LaunchShape s,
                             cudaStream_t stream) {
-    dispatch_kernel<<<s.ctas, s.warps * 32, s.smem_bytes, stream>>>(c, ws, a);
+    switch (pick_buffers(c.g)) {
+        case 4: dispatch_kernel<4><<<s.ctas, s.warps * 32, s.smem_bytes, stream>>>(c, ws, a); break;
+        case 3: dispatch_kernel<3><<<s.ctas, s.warps * 32, s.smem_bytes, stream>>>(c, ws, a); break;
+        default: dispatch_kernel<2><<<s.ctas, s.warps * 32, s.smem_bytes, stream>>>(c, ws, a); break;
+    }
     return cudaGetLastError();
 }
 
 cudaError_t configure_dispatch(int max_smem) {
-    return cudaFuncSetAttribute(dispatch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
+    cudaFuncAttributes attr;
+    cudaError_t e = cudaFuncGetAttributes(&attr, dispatch_kernel<4>);
+    if (e != cudaSuccess) return e;
+    g_dyn_smem = max_smem - (int)attr.sharedSizeBytes - 128;
+    e = cudaFuncSetAttribute(dispatch_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, g_dyn_smem);
+    if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(dispatch_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, g_dyn_smem);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(dispatch_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, g_dyn_smem);
 }
 
 }  // namespace afdep

@@ -25,7 +25,6 @@ namespace afdep {
 
 namespace {
 
-constexpr int kNB = 2;
 constexpr int kBarBytes = 512;
 constexpr int kMaxWarps = 16;
 
@@ -155,6 +154,9 @@ __global__ void __launch_bounds__(256, 1) ffn_layout_kernel(const RankCtx c, con
     }
 }
 
+// NB record buffers per warp: while record i is being scattered to its expert rows, record
+// i+1 is already being pulled into the next buffer if its arrival flag is up.
+template <int NB>
 __global__ void __launch_bounds__(kMaxWarps * 32, 1)
 receive_kernel(const RankCtx c, const FfnWs ws, const ReceiveArgs r) {
     extern __shared__ __align__(128) unsigned char smem[];
@@ -167,6 +169,7 @@ receive_kernel(const RankCtx c, const FfnWs ws, const ReceiveArgs r) {
     const unsigned ep = ptx::ld_acquire_gpu(&ws.epoch[0]) + 1u;
     const WaitCtx wc{c.status, c.poison, c.budget, c.rank, /*kernel=*/3};
     unsigned char* heap = reinterpret_cast<unsigned char*>(c.peer[c.rank]);
+    trace_stamp(c.trace, kTraceReceive, 0);
 
     bool ok = true;
     if (r.layout_ready) {
@@ -175,11 +178,12 @@ receive_kernel(const RankCtx c, const FfnWs ws, const ReceiveArgs r) {
         ok = compute_layout(c, wc, ep, L);
         if (ok && cta == 0) publish_layout(c, ws, r, L);
     }
+    trace_stamp(c.trace, kTraceReceive, 1);
 
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
-    unsigned char* bufs = smem + kBarBytes + (size_t)warp * kNB * g.rec_bytes;
+    unsigned char* bufs = smem + kBarBytes + (size_t)warp * NB * g.rec_bytes;
     if (lane == 0) {
-        for (int b = 0; b < kNB; ++b) ptx::mbar_init(&bars[warp * kNB + b], 1);
+        for (int b = 0; b < NB; ++b) ptx::mbar_init(&bars[warp * NB + b], 1);
         ptx::fence_mbar_init();
     }
     __syncwarp();
@@ -190,38 +194,70 @@ receive_kernel(const RankCtx c, const FfnWs ws, const ReceiveArgs r) {
     const int total = ok ? L.rec_prefix[A] : 0;
     const int sg = g.fp8 ? g.scale_groups : 0;
     unsigned char* rx = static_cast<unsigned char*>(r.recv_x);
-    int it = 0;
-    for (int item = cta * NW + warp; item < total; item += G * NW) {
-        int a = 0;
+    const int first = cta * NW + warp, stride = G * NW;
+    const int n_w = first < total ? (total - first + stride - 1) / stride : 0;
+
+    auto locate = [&](int i, int& a, int& slot) {
+        const int item = first + i * stride;
+        a = 0;
         while (a + 1 < A && item >= L.rec_prefix[a + 1]) ++a;
-        const int slot = item - L.rec_prefix[a];
-        bool arrived = true;
+        slot = item - L.rec_prefix[a];
+    };
+    // Start pulling record i into its ring buffer.  Non-blocking mode gives up at once when the
+    // record has not arrived; blocking mode spins (bounded).  Returns 1 issued, 0 not yet, -1 dead.
+    auto issue = [&](int i, bool blocking) -> int {
+        int a, slot;
+        locate(i, a, slot);
+        int state = 1;
         if (lane == 0) {
-            uint32_t seen = 0;
-            arrived = spin_until(wc, [&] {
-                seen = ptx::ld_acquire_sys(slot_flag + (size_t)a * C + slot);
-                return seen == ep;
-            });
-            if (!arrived) {
-                report(wc, kTimeoutRecord, g.ffn + a, ep, ep, seen, slot, total);
-                poison(wc);
+            const uint32_t* flag = slot_flag + (size_t)a * C + slot;
+            uint32_t seen = ptx::ld_acquire_sys(flag);
+            if (seen != ep) {
+                if (!blocking) {
+                    state = 0;
+                } else {
+                    const bool arrived = spin_until(wc, [&] {
+                        seen = ptx::ld_acquire_sys(flag);
+                        return seen == ep;
+                    });
+                    if (!arrived) {
+                        report(wc, kTimeoutRecord, g.ffn + a, ep, ep, seen, slot, total);
+                        poison(wc);
+                        state = -1;
+                    }
+                }
+            }
+            if (state == 1) {
+                uint64_t* bar = &bars[warp * NB + (i % NB)];
+                ptx::fence_proxy_async_global();
+                ptx::mbar_expect_tx(bar, used);
+                ptx::bulk_load(bufs + (size_t)(i % NB) * g.rec_bytes, stage + ((size_t)a * C + slot) * g.rec_bytes, used, bar);
             }
         }
-        arrived = __shfl_sync(ptx::kFullMask, arrived, 0);
-        if (!arrived) break;
-        const int b = it % kNB;
-        const unsigned parity = (it / kNB) & 1u;
-        unsigned char* buf = bufs + (size_t)b * g.rec_bytes;
-        uint64_t* bar = &bars[warp * kNB + b];
-        if (lane == 0) {
-            if (it >= kNB) ptx::bulk_wait_read<kNB - 1>();
-            ptx::fence_proxy_async_global();
-            ptx::mbar_expect_tx(bar, used);
-            ptx::bulk_load(buf, stage + ((size_t)a * C + slot) * g.rec_bytes, used, bar);
+        return __shfl_sync(ptx::kFullMask, state, 0);
+    };
+
+    int have = 0;       // 1 when record i's load has been issued ahead of time
+    for (int i = 0; i < n_w; ++i) {
+        if (!have && issue(i, true) < 0) break;
+        have = 0;
+        if (i + 1 < n_w) {
+            // Buffer (i+1) % NB was last read by the stores of record i+1-NB.
+            if (lane == 0) ptx::bulk_wait_read<NB - 2>();
+            __syncwarp();
+            const int st = issue(i + 1, false);
+            if (st < 0) break;
+            have = st;
         }
+        const int b = i % NB;
+        const unsigned parity = (i / NB) & 1u;
+        unsigned char* buf = bufs + (size_t)b * g.rec_bytes;
+        uint64_t* bar = &bars[warp * NB + b];
         bool landed = spin_until(wc, [&] { return ptx::mbar_try_wait(bar, parity); });
         landed = __all_sync(ptx::kFullMask, landed);
         if (!landed) break;
+        int a, slot;
+        locate(i, a, slot);
 
         const int* meta = reinterpret_cast<const int*>(buf + g.meta_off);
         int row = -1;
@@ -254,11 +290,11 @@ receive_kernel(const RankCtx c, const FfnWs ws, const ReceiveArgs r) {
             r.recv_src[2 * (size_t)row + 1] = src_token;
         }
         __syncwarp();
-        ++it;
     }
     if (lane == 0) ptx::bulk_wait<0>();
 
     __syncthreads();
+    trace_stamp(c.trace, kTraceReceive, 2);
     if (tid == 0) {
         __threadfence();
         if (atomicAdd(&ws.ticket[0], 1u) == (unsigned)(G - 1)) {
@@ -286,18 +322,24 @@ __device__ __forceinline__ uint4 pack_bf16x8(const float* acc) {
     return v;
 }
 
-__global__ void __launch_bounds__(kMaxWarps * 32, 1)
+constexpr int kReplyWarps = 8;   // seven reducing warps (16 loads per lane in flight) and one flag warp
+
+__global__ void __launch_bounds__(kReplyWarps * 32, 2)
 reply_kernel(const RankCtx c, const FfnWs ws, const unsigned char* __restrict__ rows, int rows_cap) {
     __shared__ LayoutSmem L;
-    __shared__ int s_rows[kMaxWarps][kMaxTopK];
+    __shared__ int s_rows[kReplyWarps][kMaxTopK];
+    __shared__ int s_done[32];
     const Geometry& g = c.g;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, NW = blockDim.x >> 5;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int ND = kReplyWarps - 1;
     const int G = gridDim.x, cta = blockIdx.x;
     const int A = g.attn, K = g.top_k, EL = g.experts_local, C = g.capacity;
     const int fi = c.role_rank;
     const unsigned ep = ptx::ld_acquire_gpu(&ws.epoch[1]) + 1u;
     const WaitCtx wc{c.status, c.poison, c.budget, c.rank, /*kernel=*/4};
     unsigned char* heap = reinterpret_cast<unsigned char*>(c.peer[c.rank]);
+    if (tid < 32) s_done[tid] = 0;
+    trace_stamp(c.trace, kTraceReply, 0);
     load_layout(c, ws, L);
     const bool dead = poisoned(wc);   // an abandoned receive leaves no layout to reply to
 
@@ -305,68 +347,114 @@ reply_kernel(const RankCtx c, const FfnWs ws, const unsigned char* __restrict__ 
     unsigned char* reply = heap + g.f_reply;
     const int total = dead ? 0 : L.rec_prefix[A];
     const int nvec = g.hidden / 8;    // 16-byte vectors per row
-    for (int item = cta * NW + warp; item < total; item += G * NW) {
-        int a = 0;
+    const int stride = G * ND;
+    auto first_of = [&](int w) { return cta * ND + w; };
+    auto count_of = [&](int w) { return first_of(w) < total ? (total - first_of(w) + stride - 1) / stride : 0; };
+    auto locate = [&](int item, int& a, int& slot) {
+        a = 0;
         while (a + 1 < A && item >= L.rec_prefix[a + 1]) ++a;
-        const int slot = item - L.rec_prefix[a];
-        const int* meta = reinterpret_cast<const int*>(stage + ((size_t)a * C + slot) * g.rec_bytes + g.meta_off);
-        int row = -1;
-        if (lane < K) {
-            const int e = __ldcg(meta + lane);
-            const int el = e - fi * EL;
-            if (e >= 0 && el >= 0 && el < EL) {
-                row = L.row_base[a * EL + el] + __ldcg(meta + K + lane);
-                if (row < 0 || row >= rows_cap) row = -1;
+        slot = item - L.rec_prefix[a];
+    };
+
+    if (warp < ND) {
+        const int n_w = count_of(warp);
+        for (int i = 0; i < n_w; ++i) {
+            int a, slot;
+            locate(first_of(warp) + i * stride, a, slot);
+            const int* meta = reinterpret_cast<const int*>(stage + ((size_t)a * C + slot) * g.rec_bytes + g.meta_off);
+            int row = -1;
+            if (lane < K) {
+                const int e = __ldcg(meta + lane);
+                const int el = e - fi * EL;
+                if (e >= 0 && el >= 0 && el < EL) {
+                    row = L.row_base[a * EL + el] + __ldcg(meta + K + lane);
+                    if (row < 0 || row >= rows_cap) row = -1;
+                }
             }
-        }
-        const unsigned hits = __ballot_sync(ptx::kFullMask, row >= 0);
-        const int nh = __popc(hits);
-        if (row >= 0) s_rows[warp][__popc(hits & ptx::lanemask_lt())] = row;
-        __syncwarp();
-        unsigned char* out = reply + ((size_t)a * C + slot) * g.row_bytes;
-        if (nh == 1) {
-            const unsigned char* src = rows + (size_t)s_rows[warp][0] * g.row_bytes;
-            for (int v = lane; v < nvec; v += 32 * 4) {
-                uint4 x[4];
+            const unsigned hits = __ballot_sync(ptx::kFullMask, row >= 0);
+            const int nh = __popc(hits);
+            if (row >= 0) s_rows[warp][__popc(hits & ptx::lanemask_lt())] = row;
+            __syncwarp();
+            unsigned char* out = reply + ((size_t)a * C + slot) * g.row_bytes;
+            if (nh == 1) {
+                const unsigned char* src = rows + (size_t)s_rows[warp][0] * g.row_bytes;
+                constexpr int U = 8;
+                for (int v = lane; v < nvec; v += 32 * U) {
+                    uint4 x[U];
 #pragma unroll
-                for (int u = 0; u < 4; ++u)
-                    if (v + u * 32 < nvec) x[u] = *reinterpret_cast<const uint4*>(src + (size_t)(v + u * 32) * 16);
-#pragma unroll
-                for (int u = 0; u < 4; ++u)
-                    if (v + u * 32 < nvec) *reinterpret_cast<uint4*>(out + (size_t)(v + u * 32) * 16) = x[u];
-            }
-        } else {
-            for (int v = lane; v < nvec; v += 32 * 2) {
-                float acc[2][8];
-#pragma unroll
-                for (int u = 0; u < 2; ++u)
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) acc[u][i] = 0.f;
-                for (int h = 0; h < nh; ++h) {
-                    const unsigned char* src = rows + (size_t)s_rows[warp][h] * g.row_bytes;
-                    uint4 x[2];
-#pragma unroll
-                    for (int u = 0; u < 2; ++u)
+                    for (int u = 0; u < U; ++u)
                         if (v + u * 32 < nvec) x[u] = *reinterpret_cast<const uint4*>(src + (size_t)(v + u * 32) * 16);
 #pragma unroll
-                    for (int u = 0; u < 2; ++u)
-                        if (v + u * 32 < nvec) acc_bf16x8(acc[u], x[u]);
+                    for (int u = 0; u < U; ++u)
+                        if (v + u * 32 < nvec) *reinterpret_cast<uint4*>(out + (size_t)(v + u * 32) * 16) = x[u];
                 }
+            } else {
+                // Rows are fetched eight at a time for two vectors per lane, so sixteen 16-byte
+                // loads are in flight per lane; the additions still happen in top-k order.
+                constexpr int U = 2, R = 8;
+                for (int v = lane; v < nvec; v += 32 * U) {
+                    float acc[U][8];
 #pragma unroll
-                for (int u = 0; u < 2; ++u)
-                    if (v + u * 32 < nvec)
-                        *reinterpret_cast<uint4*>(out + (size_t)(v + u * 32) * 16) = pack_bf16x8(acc[u]);
+                    for (int u = 0; u < U; ++u)
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) acc[u][q] = 0.f;
+                    for (int h0 = 0; h0 < nh; h0 += R) {
+                        uint4 x[R][U];
+#pragma unroll
+                        for (int j = 0; j < R; ++j) {
+                            if (h0 + j < nh) {
+                                const unsigned char* src = rows + (size_t)s_rows[warp][h0 + j] * g.row_bytes;
+#pragma unroll
+                                for (int u = 0; u < U; ++u)
+                                    if (v + u * 32 < nvec) x[j][u] = *reinterpret_cast<const uint4*>(src + (size_t)(v + u * 32) * 16);
+                            }
+                        }
+#pragma unroll
+                        for (int j = 0; j < R; ++j) {
+                            if (h0 + j < nh) {
+#pragma unroll
+                                for (int u = 0; u < U; ++u)
+                                    if (v + u * 32 < nvec) acc_bf16x8(acc[u], x[j][u]);
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int u = 0; u < U; ++u)
+                        if (v + u * 32 < nvec)
+                            *reinterpret_cast<uint4*>(out + (size_t)(v + u * 32) * 16) = pack_bf16x8(acc[u]);
+                }
             }
+            __syncwarp();      // every lane's stores are ordered before the hand-off below
+            if (lane == 0) ptx::st_release_cta_shared(&s_done[warp], i + 1);
         }
-        __syncwarp();
-        if (lane == 0) {
-            ptx::fence_acq_rel_sys();
-            uint32_t* flag = reinterpret_cast<uint32_t*>(c.peer[g.ffn + a] + g.a_reply_flag) + (size_t)fi * C + slot;
-            ptx::st_relaxed_sys(flag, ep);
+    } else {
+        // Flag warp: lane w follows reducing warp w; one system-scope fence covers every record
+        // handed over since the last one, so the fence never stalls a reducing warp.
+        const int mine = (lane < ND) ? count_of(lane) : 0;
+        int flagged = 0;
+        unsigned idle = 0;
+        const long long t_begin = clock64();
+        while (true) {
+            const int d = (lane < ND) ? ptx::ld_acquire_cta_shared(&s_done[lane]) : 0;
+            if (d > flagged) {
+                ptx::fence_acq_rel_sys();
+                for (int j = flagged; j < d; ++j) {
+                    int a, slot;
+                    locate(first_of(lane) + j * stride, a, slot);
+                    uint32_t* flag = reinterpret_cast<uint32_t*>(c.peer[g.ffn + a] + g.a_reply_flag) + (size_t)fi * C + slot;
+                    ptx::st_relaxed_sys(flag, ep);
+                }
+                flagged = d;
+                idle = 0;
+            }
+            if (__all_sync(ptx::kFullMask, flagged >= mine)) break;
+            if (++idle > 1) __nanosleep(64);
+            if ((idle & 255u) == 0 && (poisoned(wc) || clock64() - t_begin > 4 * c.budget)) break;
         }
     }
 
     __syncthreads();
+    trace_stamp(c.trace, kTraceReply, 2);
     if (tid == 0) {
         __threadfence();
         if (atomicAdd(&ws.ticket[1], 1u) == (unsigned)(G - 1)) {
@@ -382,15 +470,21 @@ reply_kernel(const RankCtx c, const FfnWs ws, const unsigned char* __restrict__ 
 // Static shared memory of the receive kernel, measured once by configure_ffn.
 static int g_receive_static = (int)sizeof(LayoutSmem) + 1024;
 
+static int receive_buffers(const Geometry& g, int max_smem) {
+    const int avail = max_smem - kBarBytes - g_receive_static;
+    return avail / (3 * g.rec_bytes) >= 4 ? 3 : 2;
+}
+
 LaunchShape receive_shape(const Geometry& g, int num_sms, int max_smem) {
     LaunchShape s{};
+    const int nb = receive_buffers(g, max_smem);
     int avail = max_smem - kBarBytes - g_receive_static;
-    int warps = avail / (kNB * g.rec_bytes);
+    int warps = avail / (nb * g.rec_bytes);
     if (warps > kMaxWarps) warps = kMaxWarps;
     if (warps < 1) warps = 1;
     s.ctas = num_sms;
     s.warps = warps;
-    s.smem_bytes = kBarBytes + warps * kNB * g.rec_bytes;
+    s.smem_bytes = kBarBytes + warps * nb * g.rec_bytes;
     return s;
 }
 
@@ -398,8 +492,8 @@ LaunchShape reply_shape(const Geometry& g, int num_sms, int max_smem) {
     (void)g;
     (void)max_smem;
     LaunchShape s{};
-    s.ctas = num_sms;
-    s.warps = kMaxWarps;
+    s.ctas = 2 * num_sms;
+    s.warps = kReplyWarps;
     s.smem_bytes = 0;
     return s;
 }
@@ -411,7 +505,12 @@ cudaError_t launch_ffn_layout(const RankCtx& c, const FfnWs& ws, const ReceiveAr
 
 cudaError_t launch_receive(const RankCtx& c, const FfnWs& ws, const ReceiveArgs& r, LaunchShape s,
                            cudaStream_t stream) {
-    receive_kernel<<<s.ctas, s.warps * 32, s.smem_bytes, stream>>>(c, ws, r);
+    // The ring depth is implied by the shape receive_shape chose.
+    const int nb = (s.smem_bytes - kBarBytes) / (s.warps * c.g.rec_bytes);
+    if (nb >= 3)
+        receive_kernel<3><<<s.ctas, s.warps * 32, s.smem_bytes, stream>>>(c, ws, r);
+    else
+        receive_kernel<2><<<s.ctas, s.warps * 32, s.smem_bytes, stream>>>(c, ws, r);
     return cudaGetLastError();
 }
 
@@ -424,10 +523,12 @@ cudaError_t launch_reply(const RankCtx& c, const FfnWs& ws, const void* rows, in
 
 cudaError_t configure_ffn(int max_smem) {
     cudaFuncAttributes attr;
-    cudaError_t e = cudaFuncGetAttributes(&attr, receive_kernel);
+    cudaError_t e = cudaFuncGetAttributes(&attr, receive_kernel<3>);
     if (e != cudaSuccess) return e;
-    g_receive_static = (int)attr.sharedSizeBytes;
-    return cudaFuncSetAttribute(receive_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    g_receive_static = (int)attr.sharedSizeBytes + 128;
+    e = cudaFuncSetAttribute(receive_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem - g_receive_static);
+    if (e != cudaSuccess) return e;
+    return cudaFuncSetAttribute(receive_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 max_smem - g_receive_static);
 }
 

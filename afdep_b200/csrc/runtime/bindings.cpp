@@ -19,6 +19,7 @@
 #include <thread>
 
 #include "afdep/kernels.h"
+#include "afdep/route_layout_api.h"
 #include "driver.hpp"
 #include "heap.hpp"
 
@@ -98,6 +99,7 @@ public:
         ctx_.poison = fl;                       // words 0..3
         ctx_.budget = (long long)(gpu_timeout_s * 1000.0 * (double)khz);
         ctx_.bounds_check = bounds_check ? 1 : 0;
+        ctx_.trace = nullptr;
         barrier_epoch_ = reinterpret_cast<unsigned*>(fl + 8);
         if (is_ffn_) {
             fws_.epoch = reinterpret_cast<unsigned*>(fl + 16);    // 3 words
@@ -305,6 +307,19 @@ public:
         return v;
     }
 
+    // Per-CTA time stamps of the exchange kernels: int64 [4 kernels][kTraceCtas][4] in
+    // nanoseconds of the GPU's global timer; pass enable=false to switch tracing off again.
+    torch::Tensor trace(bool enable) {
+        if (!enable) {
+            ctx_.trace = nullptr;
+            return trace_;
+        }
+        if (!trace_.defined())
+            trace_ = torch::zeros({4, kTraceCtas, 4}, torch::TensorOptions().dtype(torch::kInt64).device(torch::kCUDA, device_));
+        ctx_.trace = reinterpret_cast<unsigned long long*>(trace_.data_ptr<int64_t>());
+        return trace_;
+    }
+
     int64_t launches() const { return launches_; }
     int resolved_num_sms() const { return num_sms_; }
     int device_sms() const { return device_sms_; }
@@ -318,6 +333,7 @@ public:
         flags_ = torch::Tensor();
         scratch_ = torch::Tensor();
         agg_ = torch::Tensor();
+        trace_ = torch::Tensor();
         heap_->release();
         if (host_block_) cudaFreeHost(host_block_);
         host_block_ = nullptr;
@@ -348,9 +364,36 @@ private:
     unsigned* barrier_epoch_ = nullptr;
     std::unique_ptr<SymmetricHeap> heap_;
     void* host_block_ = nullptr;
-    torch::Tensor flags_, scratch_, agg_;
+    torch::Tensor flags_, scratch_, agg_, trace_;
     int64_t host_seq_ = 0, launches_ = 0;
 };
+
+// Deterministic routing layout of one source (see kernels/layout.cu).  Returns
+// (route_e [T,K], route_pos [T,K], tok_slot [T,F], counts [F+E]) as int32 tensors.
+py::tuple route_layout(const torch::Tensor& ids, int64_t num_experts, int64_t ffn_ranks) {
+    TORCH_CHECK(ids.is_cuda() && ids.dim() == 2 && ids.scalar_type() == torch::kInt64 && ids.is_contiguous(),
+                "ids must be a contiguous CUDA int64 [tokens, top_k] tensor");
+    TORCH_CHECK(ffn_ranks >= 1 && ffn_ranks <= kMaxRanks && num_experts % ffn_ranks == 0 && num_experts <= kMaxExperts,
+                "unsupported expert geometry");
+    const int64_t T = ids.size(0), K = ids.size(1);
+    TORCH_CHECK(K >= 1 && K <= kMaxTopK, "top_k out of range");
+    c10::cuda::CUDAGuard guard(ids.device());
+    auto i32 = torch::TensorOptions().dtype(torch::kInt32).device(ids.device());
+    auto scratch = torch::zeros({(int64_t)route_layout_scratch_bytes((int)num_experts, (int)ffn_ranks)},
+                                torch::TensorOptions().dtype(torch::kUInt8).device(ids.device()));
+    auto route_e = torch::empty({T, K}, i32);
+    auto route_pos = torch::empty({T, K}, i32);
+    auto tok_slot = torch::empty({T, ffn_ranks}, i32);
+    auto counts = torch::empty({ffn_ranks + num_experts}, i32);
+    int khz = 0;
+    rt_check(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, ids.get_device()), "device attribute");
+    rt_check(launch_route_layout(reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()), (int)T, (int)K,
+                                 (int)num_experts, (int)ffn_ranks, scratch.data_ptr(), route_e.data_ptr<int>(),
+                                 route_pos.data_ptr<int>(), tok_slot.data_ptr<int>(), counts.data_ptr<int>(),
+                                 (long long)khz * 1000ll * 5ll, at::cuda::getCurrentCUDAStream().stream()),
+             "route_layout launch");
+    return py::make_tuple(route_e, route_pos, tok_slot, counts);
+}
 
 }  // namespace afdep
 
@@ -359,6 +402,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.doc() = "afdep_b200 native runtime (sm_100a)";
     m.attr("max_ranks") = afdep::kMaxRanks;
     m.def("vmm_supported", [](int device) { return afdep::SymmetricHeap::vmm_supported(device); });
+    m.def("route_layout", &afdep::route_layout, py::arg("ids"), py::arg("num_experts"), py::arg("ffn_ranks"));
     py::class_<NativeBuffer>(m, "NativeBuffer")
         .def(py::init<int, int, int, int, int, int, int, bool, int, int, int, int, double, int64_t, const std::string&, bool>(),
              py::arg("rank"), py::arg("ffn"), py::arg("attn"), py::arg("hidden"), py::arg("top_k"), py::arg("num_experts"),
@@ -382,6 +426,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("status_code", &NativeBuffer::status_code)
         .def("clear_status", &NativeBuffer::clear_status)
         .def("bad_routes", &NativeBuffer::bad_routes)
+        .def("trace", &NativeBuffer::trace)
         .def("launches", &NativeBuffer::launches)
         .def("resolved_num_sms", &NativeBuffer::resolved_num_sms)
         .def("device_sms", &NativeBuffer::device_sms)

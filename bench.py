@@ -234,8 +234,20 @@ def main() -> None:
         if multi:
             buffers[0]._t._nb.barrier() if args.impl == "ours" else dist.barrier()
 
-    def step(copy_inputs: bool):
-        """One exchange in dependency order; returns a device checksum on attention ranks."""
+    phase_log: dict[str, list] = {"dispatch": [], "receive": [], "reply": [], "collect": []}
+
+    def mark(name, fn, record):
+        if not record:
+            return fn()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        out = fn()
+        b.record()
+        phase_log[name].append((a, b))
+        return out
+
+    def step(copy_inputs: bool, record: bool = False):
+        """One exchange in dependency order; returns the collected output on attention ranks."""
         result = None
         for s in ordered:
             if s["buf"].role == "attention":
@@ -244,16 +256,16 @@ def main() -> None:
                         if d is not None:
                             d.copy_(h, non_blocking=True)
                 x, ids, w, scale = s["dev"]
-                s["buf"].source_dispatch(x, ids, w, scale, bucket=T)
+                mark("dispatch", lambda: s["buf"].source_dispatch(x, ids, w, scale, bucket=T), record)
         for s in ordered:
             if s["buf"].role == "ffn":
-                rec = s["buf"].worker_receive(bucket=T)
+                rec = mark("receive", lambda: s["buf"].worker_receive(bucket=T), record)
                 rows = rec.recv_x if not cfg.is_fp8 else s["rows"]
                 s["psum"] = rec.recv_count_psum
-                s["buf"].worker_reply(rows, rec.receipt)
+                mark("reply", lambda: s["buf"].worker_reply(rows, rec.receipt), record)
         for s in ordered:
             if s["buf"].role == "attention":
-                s["out"] = s["buf"].source_collect()
+                s["out"] = mark("collect", lambda: s["buf"].source_collect(), record)
                 result = s["out"]
         return result
 
@@ -283,7 +295,7 @@ def main() -> None:
             if graph is not None and not copy_inputs:
                 graph.replay()
             else:
-                out = step(copy_inputs)
+                out = step(copy_inputs, record=(i >= warmup and not copy_inputs))
                 if copy_inputs:
                     src = out.float().sum().reshape(1) if out is not None else state[0]["psum"].float().sum().reshape(1)
                     host_result.copy_(src, non_blocking=True)
@@ -319,6 +331,16 @@ def main() -> None:
             dist.all_gather_object(allv, total)
             return max(allv)
         return total
+
+    # mean device time of each role call (kernel plus its waits), maximum over ranks
+    phases = {}
+    for name, pairs in phase_log.items():
+        local_us = 1e3 * sum(a.elapsed_time(b) for a, b in pairs) / max(1, len(pairs)) if pairs else 0.0
+        if multi:
+            allp = [None] * n
+            dist.all_gather_object(allp, local_us)
+            local_us = max(allp)
+        phases[name + "_us"] = round(local_us, 2)
 
     total_ms = reduce_max(times)
     ms_per_step = total_ms / args.steps
@@ -359,6 +381,7 @@ def main() -> None:
             "tokens_per_s": round(T * attn / (ms_per_step * 1e-3), 1),
             "per_attention_rank_GBs": round(value / attn, 3),
         },
+        "phases": phases,
         "clocks": clocks,
         "gpu_launches": launches,
         "wall_s_timed_region": round(t_wall1 - t_wall0, 3),
