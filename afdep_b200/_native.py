@@ -168,6 +168,11 @@ def build(verbose: bool = False) -> Path:
             _run(link)
             os.replace(tmp, target)
             shutil.rmtree(work, ignore_errors=True)
+            for old in stale_libraries():     # keep the tree (and what travels with it) small
+                try:
+                    old.unlink()
+                except OSError:
+                    pass
             return target
         finally:
             fcntl.flock(lock, fcntl.LOCK_UN)

@@ -1,17 +1,22 @@
 // Deterministic routing layout of one source rank, computed inside a running grid.
 //
-// Every CTA owns a contiguous chunk of tokens.  Its warps rank each (token, k) choice among
-// the earlier choices of the same expert and each (token, FFN rank) record among the earlier
-// records for that rank: first inside the warp's sub-range (match-any), then across the
-// CTA's warps (shared-memory scan), then across CTAs (decoupled look-back over epoch-tagged
-// aggregates in global scratch).  Outputs, final when the function returns:
+// Every (token, k) choice is ranked among the earlier choices of the same expert and every
+// (token, FFN rank) record among the earlier records for that rank, in token order:
 //   route_e[t][k]   expert id or -1 (skipped, or the whole token was illegal)
 //   route_pos[t][k] number of earlier choices of that expert by this source
 //   tok_slot[t][f]  number of earlier tokens of this source with a record for FFN rank f, or -1
-// and, in shared memory, the CTA's own totals `tot[col]` and the sum over earlier CTAs
-// `lb[col]` (columns: [0, F) records per FFN rank, then one per expert), so the last CTA
-// holds the source's totals.  Illegal routes (id outside [-1, E) at full 64-bit width, or an
-// expert twice in one token) are reported, not trapped.
+// plus the source's totals per column (columns: [0, F) records per FFN rank, then one per
+// expert).  Illegal routes (id outside [-1, E) at full 64-bit width, or an expert twice in
+// one token) are reported, not trapped, and publish nothing.
+//
+// Two ways to split the work:
+//   distributed  every CTA owns a contiguous chunk of tokens; warps rank inside their
+//                sub-range (match-any), a shared-memory scan joins the warps, a decoupled
+//                look-back over epoch-tagged aggregates in global scratch joins the CTAs.
+//   redundant    for small inputs every CTA ranks ALL tokens itself and keeps the part it
+//                owns: no traffic between CTAs at all, which is what decode-sized batches want.
+// Results for the CTA's own tokens can stay in a shared-memory table (`local`), so the caller's
+// next phase reads them without a trip through global memory; global outputs are written once.
 //
 // Covers what the reference spreads over its notify warps, its deterministic prologue and
 // its route guard (deep_ep/include/deep_ep/impls/dispatch.cuh:93-157,
@@ -24,35 +29,68 @@
 namespace afdep {
 
 struct RouteLayoutOut {
-    int* route_e;
-    int* route_pos;
+    int* route_e;     // may be null when the caller keeps the table in shared memory
+    int* route_pos;   // may be null, as above
     int* tok_slot;
 };
 
-// Shared-memory ints the function needs at `scratch`.
+struct RouteLayoutJob {
+    const long long* ids;
+    int T, K, E, EL, F;
+    unsigned ep;                 // tag of this launch in the aggregate array
+    unsigned long long* agg;     // [gridDim.x][F + E], distributed mode only
+    RouteLayoutOut out;
+    int* wh;                     // smem [warps][F + E]
+    int* tot;                    // smem [F + E]: this CTA's totals
+    int* lb;                     // smem [F + E]: sum over earlier CTAs (zero in redundant mode)
+    int* local;                  // smem [tokens][2K + F] (e, pos, slot) or null
+    int redundant;               // 1: every CTA ranks all tokens
+};
+
 __host__ __device__ __forceinline__ int route_layout_scratch_ints(int warps, int ncols) { return (warps + 2) * ncols; }
 
-// Returns false (uniformly for the CTA) if the look-back was abandoned.
-__device__ __forceinline__ bool route_layout_phase(const long long* __restrict__ ids, int T, int K, int E, int EL, int F,
-                                                    unsigned ep, unsigned long long* agg, const RouteLayoutOut& o,
-                                                    int* scratch, const WaitCtx& wc, int** tot_out, int** lb_out) {
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, NW = blockDim.x >> 5;
-    const int G = gridDim.x, cta = blockIdx.x;
-    const int ncols = F + E;
+// Token range a CTA owns.
+__device__ __forceinline__ void route_layout_chunk(int T, int& t0, int& t1) {
+    const int G = gridDim.x;
     const int chunk = (T + G - 1) / G;
-    const int t0 = min(T, cta * chunk), t1 = min(T, t0 + chunk);
-    const int n = t1 - t0;
-    const int sub = (n + NW - 1) / NW;
-    const int w0 = min(t1, t0 + warp * sub), w1 = min(t1, w0 + sub);
+    t0 = min(T, (int)blockIdx.x * chunk);
+    t1 = min(T, t0 + chunk);
+}
 
-    int* wh = scratch;              // [NW][ncols] per-warp histograms, later exclusive warp bases
-    int* tot = wh + NW * ncols;     // [ncols] CTA totals
-    int* lb = tot + ncols;          // [ncols] sum over earlier CTAs
+// Row of the shared-memory table that holds token t.
+__device__ __forceinline__ int route_layout_local_row(const RouteLayoutJob& j, int t, int t0) {
+    return j.redundant ? t : t - t0;
+}
+
+// Returns false (uniformly for the CTA) if the look-back was abandoned.  On return the CTA
+// holds totals in tot/lb (the last CTA of a distributed run, every CTA of a redundant run,
+// has the source's totals as lb + tot).
+__device__ __forceinline__ bool route_layout_phase(const RouteLayoutJob& j, const WaitCtx& wc) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, NW = blockDim.x >> 5;
+    const int cta = blockIdx.x;
+    const int T = j.T, K = j.K, E = j.E, EL = j.EL, F = j.F;
+    const int ncols = F + E;
+    const int LW = 2 * K + F;                 // ints per row of the local table
+    int t0, t1;
+    route_layout_chunk(T, t0, t1);
+    // range this CTA ranks, and the part of it this warp ranks
+    const int r0 = j.redundant ? 0 : t0, r1 = j.redundant ? T : t1;
+    const int n = r1 - r0;
+    const int sub = (n + NW - 1) / NW;
+    const int w0 = min(r1, r0 + warp * sub), w1 = min(r1, w0 + sub);
+
+    int* wh = j.wh;
     __shared__ int s_dead;
-    *tot_out = tot;
-    *lb_out = lb;
-    for (int i = tid; i < (NW + 2) * ncols; i += blockDim.x) wh[i] = 0;
-    for (int i = tid; i < n * F; i += blockDim.x) o.tok_slot[(size_t)t0 * F + i] = -1;
+    for (int i = tid; i < NW * ncols; i += blockDim.x) wh[i] = 0;
+    for (int i = tid; i < ncols; i += blockDim.x) {
+        j.tot[i] = 0;
+        j.lb[i] = 0;
+    }
+    if (j.local != nullptr) {
+        for (int i = tid; i < n * F; i += blockDim.x) j.local[(i / F) * LW + 2 * K + (i % F)] = -1;
+    } else {
+        for (int i = tid; i < n * F; i += blockDim.x) j.out.tok_slot[(size_t)r0 * F + i] = -1;
+    }
     if (tid == 0) s_dead = 0;
     __syncthreads();
 
@@ -62,7 +100,6 @@ __device__ __forceinline__ bool route_layout_phase(const long long* __restrict__
         const bool lane_on = tl < tpb;
         const unsigned kmask = (K == 32) ? 0xffffffffu : ((1u << K) - 1u);
         const unsigned grp = lane_on ? (kmask << (tl * K)) : 0u;
-        const unsigned lt = ptx::lanemask_lt();
         int* my = wh + warp * ncols;
         constexpr int U = 4;                    // steps whose ids are fetched together
         for (int tb0 = w0; tb0 < w1; tb0 += tpb * U) {
@@ -70,7 +107,7 @@ __device__ __forceinline__ bool route_layout_phase(const long long* __restrict__
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const int t = tb0 + u * tpb + tl;
-                idv[u] = (lane_on && t < w1) ? ids[(size_t)t * K + k] : -1ll;
+                idv[u] = (lane_on && t < w1) ? j.ids[(size_t)t * K + k] : -1ll;
             }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
@@ -82,50 +119,66 @@ __device__ __forceinline__ bool route_layout_phase(const long long* __restrict__
                 // Range check at full width, before narrowing to int.
                 bool bad = in && (id < -1ll || id >= (long long)E);
                 int e = (in && !bad && id >= 0) ? (int)id : -1;
-                int key = (e >= 0) ? (tl * kMaxExperts + e) : -(lane + 1);
-                unsigned peers = __match_any_sync(ptx::kFullMask, key);
-                if (e >= 0 && __popc(peers) > 1) bad = true;      // expert repeated in a token
+                int f = (e >= 0) ? e / EL : -1;
+                // Compare against the token's other choices (K - 1 shuffles): an expert chosen
+                // twice makes the token illegal; the lowest k of an FFN rank leads its record.
+                // (match.any would do this in one instruction, but its cost grows with the number
+                // of distinct keys, and here nearly all 32 are distinct.)
+                bool lead = e >= 0;
+                for (int d = 1; d < K; ++d) {
+                    int sk = k + d;
+                    if (sk >= K) sk -= K;
+                    const int src = (tl * K + sk) & 31;
+                    const int oe = __shfl_sync(ptx::kFullMask, e, src);
+                    const int of = __shfl_sync(ptx::kFullMask, f, src);
+                    if (e >= 0 && oe == e) bad = true;
+                    if (sk < k && of == f) lead = false;
+                }
                 const unsigned badmask = __ballot_sync(ptx::kFullMask, bad);
-                if (bad) {
-                    report(wc, kBadRoute, -1, ep, t, id, k, 0);
+                if (bad && (!j.redundant || cta == 0)) {
+                    report(wc, kBadRoute, -1, j.ep, t, id, k, 0);
                     atomicAdd(&wc.poison[kBadRoutes], 1);
                 }
-                if (badmask & grp) e = -1;      // an illegal token publishes nothing
-
-                // rank of this choice among the warp's earlier choices of the same expert
-                key = (e >= 0) ? e : -(lane + 1);
-                peers = __match_any_sync(ptx::kFullMask, key);
-                const int rank_e = __popc(peers & lt);
-                int pos = -1;
-                if (e >= 0) pos = my[F + e] + rank_e;
-                __syncwarp();
-                if (e >= 0 && rank_e == 0) my[F + e] += __popc(peers);
-
-                // one record per (token, FFN rank): the lowest lane of the pair claims a slot
-                const int f = (e >= 0) ? e / EL : -1;
-                key = (e >= 0) ? (tl * 64 + f) : -(lane + 1);
-                const unsigned ptf = __match_any_sync(ptx::kFullMask, key);
-                const bool lead = (e >= 0) && ((ptf & lt) == 0u);
-                key = lead ? f : -(lane + 1);
-                const unsigned pf = __match_any_sync(ptx::kFullMask, key);
-                const int rank_f = __popc(pf & lt);
-                int slot = -1;
-                if (lead) slot = my[f] + rank_f;
-                __syncwarp();
-                if (lead && rank_f == 0) my[f] += __popc(pf);
-                __syncwarp();
-
-                if (in) {
-                    o.route_e[(size_t)t * K + k] = e;
-                    o.route_pos[(size_t)t * K + k] = pos;
+                if (badmask & grp) {            // an illegal token publishes nothing
+                    e = -1;
+                    f = -1;
                 }
-                if (lead) o.tok_slot[(size_t)t * F + f] = slot;
+                lead = lead && e >= 0;
+                // Ranks: one token at a time, so no two lanes ever touch the same counter (a legal
+                // token names every expert, hence every FFN-rank leader, at most once).
+                int pos = -1, slot = -1;
+                for (int s = 0; s < tpb; ++s) {
+                    if (tl == s && e >= 0) {
+                        pos = my[F + e];
+                        my[F + e] = pos + 1;
+                    }
+                    if (tl == s && lead) {
+                        slot = my[f];
+                        my[f] = slot + 1;
+                    }
+                    __syncwarp();
+                }
+
+                if (j.local != nullptr) {
+                    int* row = j.local + (size_t)(t - r0) * LW;
+                    if (in) {
+                        row[k] = e;
+                        row[K + k] = pos;
+                    }
+                    if (lead) row[2 * K + f] = slot;
+                } else {
+                    if (in) {
+                        j.out.route_e[(size_t)t * K + k] = e;
+                        j.out.route_pos[(size_t)t * K + k] = pos;
+                    }
+                    if (lead) j.out.tok_slot[(size_t)t * F + f] = slot;
+                }
             }
         }
     }
     __syncthreads();
 
-    // exclusive scan over the CTA's warps, publish the CTA aggregate
+    // exclusive scan over the CTA's warps; in distributed mode publish the CTA aggregate
     for (int col = tid; col < ncols; col += blockDim.x) {
         int run = 0;
         for (int w = 0; w < NW; ++w) {
@@ -133,12 +186,13 @@ __device__ __forceinline__ bool route_layout_phase(const long long* __restrict__
             wh[w * ncols + col] = run;
             run += v;
         }
-        tot[col] = run;
-        ptx::st_relaxed_gpu_u64(&agg[(size_t)cta * ncols + col], ((unsigned long long)ep << 32) | (unsigned)run);
+        j.tot[col] = run;
+        if (!j.redundant)
+            ptx::st_relaxed_gpu_u64(&j.agg[(size_t)cta * ncols + col], ((unsigned long long)j.ep << 32) | (unsigned)run);
     }
 
     // decoupled look-back: sum the aggregates of all earlier CTAs
-    {
+    if (!j.redundant) {
         constexpr int U = 8;
         const int total = cta * ncols;
         bool ok = true;
@@ -147,20 +201,20 @@ __device__ __forceinline__ bool route_layout_phase(const long long* __restrict__
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const int idx = base + u * blockDim.x;
-                v[u] = (idx < total) ? ptx::ld_relaxed_gpu_u64(&agg[idx]) : 0ull;
+                v[u] = (idx < total) ? ptx::ld_relaxed_gpu_u64(&j.agg[idx]) : 0ull;
             }
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const int idx = base + u * blockDim.x;
                 if (idx >= total) break;
-                if ((unsigned)(v[u] >> 32) != ep) {
+                if ((unsigned)(v[u] >> 32) != j.ep) {
                     unsigned long long vv = v[u];
                     ok = spin_until(wc, [&] {
-                        vv = ptx::ld_relaxed_gpu_u64(&agg[idx]);
-                        return (unsigned)(vv >> 32) == ep;
+                        vv = ptx::ld_relaxed_gpu_u64(&j.agg[idx]);
+                        return (unsigned)(vv >> 32) == j.ep;
                     });
                     if (!ok) {
-                        report(wc, kTimeoutLookback, idx / ncols, ep, ep, (long long)(vv >> 32), cta, 0);
+                        report(wc, kTimeoutLookback, idx / ncols, j.ep, j.ep, (long long)(vv >> 32), cta, 0);
                         poison(wc);
                         s_dead = 1;
                         break;
@@ -168,30 +222,63 @@ __device__ __forceinline__ bool route_layout_phase(const long long* __restrict__
                     v[u] = vv;
                 }
                 const int cnt = (int)(unsigned)v[u];
-                if (cnt) atomicAdd(&lb[idx % ncols], cnt);
+                if (cnt) atomicAdd(&j.lb[idx % ncols], cnt);
             }
         }
     }
     __syncthreads();
 
-    // fix-up: warp-local ranks -> global pos / slot
+    // fix-up: warp-local ranks -> global pos / slot, for the tokens this warp ranked
     {
         const int* my = wh + warp * ncols;
-        const int cntk = (w1 - w0) * K;
-        for (int i = lane; i < cntk; i += 32) {
-            const size_t idx = (size_t)w0 * K + i;
-            const int e = o.route_e[idx];
-            if (e >= 0) o.route_pos[idx] += my[F + e] + lb[F + e];
-        }
-        const int cntf = (w1 - w0) * F;
-        for (int i = lane; i < cntf; i += 32) {
-            const size_t idx = (size_t)w0 * F + i;
-            const int f = i % F;
-            const int s = o.tok_slot[idx];
-            if (s >= 0) o.tok_slot[idx] = s + my[f] + lb[f];
+        const int* lb = j.lb;
+        if (j.local != nullptr) {
+            const int cnt = (w1 - w0) * LW;
+            for (int i = lane; i < cnt; i += 32) {
+                int* row = j.local + (size_t)(w0 - r0 + i / LW) * LW;
+                const int c = i % LW;
+                if (c >= K && c < 2 * K) {
+                    const int e = row[c - K];
+                    if (e >= 0) row[c] += my[F + e] + lb[F + e];
+                } else if (c >= 2 * K) {
+                    const int f = c - 2 * K;
+                    if (row[c] >= 0) row[c] += my[f] + lb[f];
+                }
+            }
+        } else {
+            const int cntk = (w1 - w0) * K;
+            for (int i = lane; i < cntk; i += 32) {
+                const size_t idx = (size_t)w0 * K + i;
+                const int e = j.out.route_e[idx];
+                if (e >= 0) j.out.route_pos[idx] += my[F + e] + lb[F + e];
+            }
+            const int cntf = (w1 - w0) * F;
+            for (int i = lane; i < cntf; i += 32) {
+                const size_t idx = (size_t)w0 * F + i;
+                const int f = i % F;
+                const int s = j.out.tok_slot[idx];
+                if (s >= 0) j.out.tok_slot[idx] = s + my[f] + lb[f];
+            }
         }
     }
     __syncthreads();
+
+    // the shared-memory table is final: write the global copies of the tokens this CTA owns
+    if (j.local != nullptr) {
+        const int own = t1 - t0;
+        for (int i = tid; i < own * F; i += blockDim.x) {
+            const int t = t0 + i / F, f = i % F;
+            j.out.tok_slot[(size_t)t * F + f] = j.local[(size_t)route_layout_local_row(j, t, t0) * LW + 2 * K + f];
+        }
+        if (j.out.route_e != nullptr) {
+            for (int i = tid; i < own * K; i += blockDim.x) {
+                const int t = t0 + i / K, k = i % K;
+                const int* row = j.local + (size_t)route_layout_local_row(j, t, t0) * LW;
+                j.out.route_e[(size_t)t * K + k] = row[k];
+                j.out.route_pos[(size_t)t * K + k] = row[K + k];
+            }
+        }
+    }
     return s_dead == 0;
 }
 

@@ -29,22 +29,34 @@ namespace afdep {
 
 namespace {
 
-constexpr int kBarBytes = 1024;   // mbarrier area at the start of dynamic shared memory
+constexpr int kBarBytes = 1024;   // mbarriers and hand-off counters at the start of dynamic shared memory
 constexpr int kMaxWarps = 16;
 constexpr int kMaxCtas = 160;
+constexpr int kMaxRouteBytes = 64 * 1024;   // largest routing table kept in shared memory
+constexpr int kRedundantEntries = 4096;     // every CTA ranks all tokens up to this many (token, k) pairs
 
-// NB record buffers per warp form a ring: while token i is being stored, token i+1 is
-// already loading, and the arrival flags of token i-(NB-2) are released once its store group
-// has completed.  NB = 2 degenerates to load -> store -> wait -> flag.
+// How a launch is laid out; computed on the host, identical for every CTA.
+struct DispatchPlan {
+    int ctas, warps, nb, smem_bytes;
+    int route_rows;      // rows of the shared-memory routing table, 0: keep it in global memory
+    int redundant;       // 1: every CTA ranks all tokens (no traffic between CTAs)
+    int route_bytes;     // bytes reserved for the table
+    int totals_bytes;    // bytes reserved for tot/lb
+};
+
+// NB record buffers per data warp form a ring: while token i is being stored, token i+1 is
+// already loading, and token i-(NB-2) is handed to the flag warp once its store group has
+// completed.  NB = 2 degenerates to load -> store -> wait -> hand off.
 template <int NB>
 __global__ void __launch_bounds__(kMaxWarps * 32, 1)
-dispatch_kernel(const RankCtx c, const AttnWs ws, const DispatchArgs a) {
-    constexpr int L = NB - 2;     // how many tokens the flag release lags behind the stores
+dispatch_kernel(const RankCtx c, const AttnWs ws, const DispatchArgs a, const DispatchPlan plan) {
+    constexpr int L = NB - 2;     // how many tokens the hand-off lags behind the stores
     extern __shared__ __align__(128) unsigned char smem[];
     const Geometry& g = c.g;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, NW = blockDim.x >> 5;
     const int G = gridDim.x, cta = blockIdx.x;
     const int F = g.ffn, K = g.top_k, E = g.num_experts, EL = g.experts_local, C = g.capacity;
+    const int ncols = F + E, LW = 2 * K + F;
     const int ai = c.role_rank;
     const unsigned ep = ptx::ld_acquire_gpu(&ws.epoch[0]) + 1u;
     const WaitCtx wc{c.status, c.poison, c.budget, c.rank, /*kernel=*/1};
@@ -52,51 +64,54 @@ dispatch_kernel(const RankCtx c, const AttnWs ws, const DispatchArgs a) {
     trace_stamp(c.trace, kTraceDispatch, 0);
 
     const int T = a.T;
-    const int chunk = (T + G - 1) / G;
-    const int t0 = min(T, cta * chunk), t1 = min(T, t0 + chunk);
+    int t0, t1;
+    route_layout_chunk(T, t0, t1);
+
+    // shared memory: [bars | routing table | totals | overlay: layout histograms, then record buffers]
+    int* local = plan.route_rows ? reinterpret_cast<int*>(smem + kBarBytes) : nullptr;
+    int* tot = reinterpret_cast<int*>(smem + kBarBytes + plan.route_bytes);
+    int* lb = tot + ncols;
+    unsigned char* overlay = smem + kBarBytes + plan.route_bytes + plan.totals_bytes;
 
     // ------------------------------------------------------------------ phase 1: layout
-    int *tot = nullptr, *lb = nullptr;
-    const RouteLayoutOut lo{ws.route_e, ws.route_pos, ws.tok_slot};
-    bool alive = route_layout_phase(a.ids, T, K, E, EL, F, ep, ws.agg, lo, reinterpret_cast<int*>(smem + kBarBytes), wc,
-                                    &tot, &lb);
-
-    // The last CTA now holds this source's totals: push them to the FFN ranks.
-    if (cta == G - 1 && alive) {
-        const int cs = cnt_stride(g);
-        for (int idx = tid; idx < F * (EL + 1); idx += blockDim.x) {
-            const int f = idx / (EL + 1), el = idx - f * (EL + 1);
-            const int col = (el < EL) ? (F + f * EL + el) : f;
-            int* dst = reinterpret_cast<int*>(c.peer[f] + g.f_cnt) + (size_t)ai * cs + el;
-            *reinterpret_cast<volatile int*>(dst) = lb[col] + tot[col];
-        }
-        __syncthreads();
-        if (tid < F) {
-            ptx::fence_acq_rel_sys();
-            ptx::st_relaxed_sys(reinterpret_cast<uint32_t*>(c.peer[tid] + g.f_cnt_flag) + ai * 32, ep);
-        }
-    }
+    RouteLayoutJob job;
+    job.ids = a.ids;
+    job.T = T;
+    job.K = K;
+    job.E = E;
+    job.EL = EL;
+    job.F = F;
+    job.ep = ep;
+    job.agg = ws.agg;
+    job.out = RouteLayoutOut{local ? nullptr : ws.route_e, local ? nullptr : ws.route_pos, ws.tok_slot};
+    job.wh = reinterpret_cast<int*>(overlay);
+    job.tot = tot;
+    job.lb = lb;
+    job.local = local;
+    job.redundant = plan.redundant;
+    const bool alive = route_layout_phase(job, wc);
     // Shared memory changes hands from generic-proxy scratch to bulk-copy buffers.
     ptx::fence_proxy_async_smem();
-    __syncthreads();
-    trace_stamp(c.trace, kTraceDispatch, 1);
 
     // ------------------------------------------------------------------ phase 2: push
-    // Warps [0, ND) move data; the last warp releases arrival flags.
+    // Warps [0, ND) move data; the last warp releases counts and arrival flags.
     const int ND = NW - 1;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
     int* done_cnt = reinterpret_cast<int*>(smem + kBarBytes - 128);   // [ND] tokens completed per data warp
-    unsigned char* bufs = smem + kBarBytes + (size_t)warp * NB * g.rec_bytes;
+    unsigned char* bufs = overlay + (size_t)warp * NB * g.rec_bytes;
     if (warp < ND && lane == 0) {
         for (int b = 0; b < NB; ++b) ptx::mbar_init(&bars[warp * NB + b], 1);
         ptx::fence_mbar_init();
     }
     if (tid < 32) done_cnt[tid] = 0;
     __syncthreads();
+    trace_stamp(c.trace, kTraceDispatch, 1);
 
     const unsigned char* xb = static_cast<const unsigned char*>(a.x);
     const int sg = g.fp8 ? g.scale_groups : 0;
     auto tokens_of = [&](int w) { return (alive && t0 + w < t1) ? (t1 - (t0 + w) + ND - 1) / ND : 0; };
+    auto local_row = [&](int t) { return local + (size_t)(plan.redundant ? t : t - t0) * LW; };
+    auto slot_of = [&](int t, int f) { return local ? local_row(t)[2 * K + f] : ws.tok_slot[(size_t)t * F + f]; };
 
     if (warp < ND) {
         const int first = t0 + warp;
@@ -106,7 +121,7 @@ dispatch_kernel(const RankCtx c, const AttnWs ws, const DispatchArgs a) {
         // A(i): start loading token i into its ring buffer and append its metadata.
         auto stage = [&](int i, int& slot, unsigned& mask) {
             const int t = first + i * ND;
-            slot = (lane < F) ? ws.tok_slot[(size_t)t * F + lane] : -1;
+            slot = (lane < F) ? slot_of(t, lane) : -1;
             mask = __ballot_sync(ptx::kFullMask, slot >= 0);
             if (mask == 0) return;
             unsigned char* buf = bufs + (size_t)(i % NB) * g.rec_bytes;
@@ -117,8 +132,14 @@ dispatch_kernel(const RankCtx c, const AttnWs ws, const DispatchArgs a) {
             }
             int* meta = reinterpret_cast<int*>(buf + g.meta_off);
             if (lane < K) {
-                meta[lane] = ws.route_e[(size_t)t * K + lane];
-                meta[K + lane] = ws.route_pos[(size_t)t * K + lane];
+                if (local) {
+                    const int* row = local_row(t);
+                    meta[lane] = row[lane];
+                    meta[K + lane] = row[K + lane];
+                } else {
+                    meta[lane] = ws.route_e[(size_t)t * K + lane];
+                    meta[K + lane] = ws.route_pos[(size_t)t * K + lane];
+                }
                 reinterpret_cast<float*>(meta)[2 * K + lane] = a.weights[(size_t)t * K + lane];
             }
             if (lane == 0) meta[3 * K] = t;
@@ -175,7 +196,24 @@ dispatch_kernel(const RankCtx c, const AttnWs ws, const DispatchArgs a) {
             ptx::st_release_cta_shared(&done_cnt[warp], ok ? n_w : -1);
         }
     } else {
-        // Flag warp: lane w follows data warp w.
+        // Flag warp.  First, in the CTA that holds the source's totals, the count "all-to-all":
+        // per-expert counts and the record count go to every FFN rank ahead of the payload flags.
+        if (cta == G - 1 && alive) {
+            const int cs = cnt_stride(g);
+            for (int idx = lane; idx < F * (EL + 1); idx += 32) {
+                const int f = idx / (EL + 1), el = idx - f * (EL + 1);
+                const int col = (el < EL) ? (F + f * EL + el) : f;
+                int* dst = reinterpret_cast<int*>(c.peer[f] + g.f_cnt) + (size_t)ai * cs + el;
+                *reinterpret_cast<volatile int*>(dst) = lb[col] + tot[col];
+            }
+            __syncwarp();
+            if (lane < F) {
+                ptx::fence_acq_rel_sys();
+                ptx::st_relaxed_sys(reinterpret_cast<uint32_t*>(c.peer[lane] + g.f_cnt_flag) + ai * 32, ep);
+            }
+        }
+        // Then lane w follows data warp w: one system-scope fence covers every token handed
+        // over since the last one, so the fence never stalls a data warp.
         const int mine = (lane < ND) ? tokens_of(lane) : 0;
         int flagged = 0;
         bool aborted = false;
@@ -192,7 +230,7 @@ dispatch_kernel(const RankCtx c, const AttnWs ws, const DispatchArgs a) {
                 for (int j = flagged; j < d; ++j) {
                     const int t = t0 + lane + j * ND;
                     for (int f = 0; f < F; ++f) {
-                        const int s = ws.tok_slot[(size_t)t * F + f];
+                        const int s = slot_of(t, f);
                         if (s >= 0 && s < C)
                             ptx::st_relaxed_sys(reinterpret_cast<uint32_t*>(c.peer[f] + g.f_slot_flag) + (size_t)ai * C + s, ep);
                     }
@@ -223,12 +261,47 @@ dispatch_kernel(const RankCtx c, const AttnWs ws, const DispatchArgs a) {
 // Opt-in shared memory left for the dynamic part, set by configure_dispatch.
 int g_dyn_smem = 227 * 1024 - 256;
 
-int pick_buffers(const Geometry& g) {
-    // Deepest ring that still leaves enough warps per CTA to hide the layout phase.
+int align128(int v) { return (v + 127) / 128 * 128; }
+
+DispatchPlan plan_dispatch(const Geometry& g, int tokens, int num_sms) {
+    DispatchPlan p{};
+    const int ncols = g.ffn + g.num_experts;
+    const int LW = 2 * g.top_k + g.ffn;
     const int avail = g_dyn_smem - kBarBytes;
-    if (avail / (4 * g.rec_bytes) >= 6) return 4;
-    if (avail / (3 * g.rec_bytes) >= 3) return 3;
-    return 2;
+    p.totals_bytes = align128(2 * ncols * 4);
+    // Ring depth from the record size alone: the deepest that keeps enough warps per CTA.
+    const int room = avail - p.totals_bytes;
+    p.nb = (room / (4 * g.rec_bytes) >= 6) ? 4 : (room / (3 * g.rec_bytes) >= 3) ? 3 : 2;
+    int data_warps = room / (p.nb * g.rec_bytes);
+    if (data_warps > kMaxWarps - 1) data_warps = kMaxWarps - 1;
+    if (data_warps < 1) data_warps = 1;
+    int ctas = num_sms < kMaxCtas ? num_sms : kMaxCtas;
+    int want = (tokens + data_warps - 1) / data_warps;   // no more CTAs than warp-sized groups of tokens
+    if (want < 1) want = 1;
+    if (ctas > want) ctas = want;
+    if (ctas < 1) ctas = 1;
+    p.ctas = ctas;
+    // Routing table in shared memory when it is small enough.
+    const int chunk = (tokens + ctas - 1) / ctas;
+    p.redundant = (tokens * g.top_k <= kRedundantEntries && tokens * LW * 4 <= kMaxRouteBytes && ctas > 1) ? 1 : 0;
+    const int rows = p.redundant ? tokens : chunk;
+    if (rows > 0 && rows * LW * 4 <= kMaxRouteBytes) {
+        p.route_rows = rows;
+        p.route_bytes = align128(rows * LW * 4);
+    } else {
+        p.redundant = 0;
+    }
+    data_warps = (room - p.route_bytes) / (p.nb * g.rec_bytes);
+    if (data_warps > kMaxWarps - 1) data_warps = kMaxWarps - 1;
+    if (data_warps < 1) data_warps = 1;
+    int warps = data_warps + 1;          // plus the flag warp
+    // The layout histograms share the overlay with the record buffers.
+    while (warps > 2 && p.route_bytes + p.totals_bytes + warps * ncols * 4 > avail) --warps;
+    p.warps = warps;
+    const int p1 = warps * ncols * 4;
+    const int p2 = (warps - 1) * p.nb * g.rec_bytes;
+    p.smem_bytes = kBarBytes + p.route_bytes + p.totals_bytes + (p1 > p2 ? p1 : p2);
+    return p;
 }
 
 }  // namespace
@@ -236,37 +309,18 @@ int pick_buffers(const Geometry& g) {
 int max_dispatch_ctas() { return kMaxCtas; }
 
 LaunchShape dispatch_shape(const Geometry& g, int tokens, int num_sms, int max_smem) {
-    LaunchShape s{};
-    const int ncols = g.ffn + g.num_experts;
     (void)max_smem;
-    const int max_dyn = g_dyn_smem;
-    const int nb = pick_buffers(g);
-    int data_warps = (max_dyn - kBarBytes) / (nb * g.rec_bytes);
-    if (data_warps > kMaxWarps - 1) data_warps = kMaxWarps - 1;
-    if (data_warps < 1) data_warps = 1;
-    int warps = data_warps + 1;          // plus the flag warp
-    // Phase 1 scratch must fit too.
-    while (warps > 2 && kBarBytes + route_layout_scratch_ints(warps, ncols) * 4 > max_dyn) --warps;
-    int ctas = num_sms < kMaxCtas ? num_sms : kMaxCtas;
-    // No point in more CTAs than there are warp-sized groups of tokens.
-    int want = (tokens + warps - 2) / (warps - 1);
-    if (want < 1) want = 1;
-    if (ctas > want) ctas = want;
-    if (ctas < 1) ctas = 1;
-    s.ctas = ctas;
-    s.warps = warps;
-    const int p1 = kBarBytes + route_layout_scratch_ints(warps, ncols) * 4;
-    const int p2 = kBarBytes + (warps - 1) * nb * g.rec_bytes;
-    s.smem_bytes = p1 > p2 ? p1 : p2;
-    return s;
+    const DispatchPlan p = plan_dispatch(g, tokens, num_sms);
+    return LaunchShape{p.ctas, p.warps, p.smem_bytes};
 }
 
 cudaError_t launch_dispatch(const RankCtx& c, const AttnWs& ws, const DispatchArgs& a, LaunchShape s,
                             cudaStream_t stream) {
-    switch (pick_buffers(c.g)) {
-        case 4: dispatch_kernel<4><<<s.ctas, s.warps * 32, s.smem_bytes, stream>>>(c, ws, a); break;
-        case 3: dispatch_kernel<3><<<s.ctas, s.warps * 32, s.smem_bytes, stream>>>(c, ws, a); break;
-        default: dispatch_kernel<2><<<s.ctas, s.warps * 32, s.smem_bytes, stream>>>(c, ws, a); break;
+    const DispatchPlan p = plan_dispatch(c.g, a.T, s.ctas);
+    switch (p.nb) {
+        case 4: dispatch_kernel<4><<<p.ctas, p.warps * 32, p.smem_bytes, stream>>>(c, ws, a, p); break;
+        case 3: dispatch_kernel<3><<<p.ctas, p.warps * 32, p.smem_bytes, stream>>>(c, ws, a, p); break;
+        default: dispatch_kernel<2><<<p.ctas, p.warps * 32, p.smem_bytes, stream>>>(c, ws, a, p); break;
     }
     return cudaGetLastError();
 }

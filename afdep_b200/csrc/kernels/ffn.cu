@@ -347,27 +347,39 @@ reply_kernel(const RankCtx c, const FfnWs ws, const unsigned char* __restrict__ 
     unsigned char* reply = heap + g.f_reply;
     const int total = dead ? 0 : L.rec_prefix[A];
     const int nvec = g.hidden / 8;    // 16-byte vectors per row
-    const int stride = G * ND;
-    auto first_of = [&](int w) { return cta * ND + w; };
-    auto count_of = [&](int w) { return first_of(w) < total ? (total - first_of(w) + stride - 1) / stride : 0; };
     auto locate = [&](int item, int& a, int& slot) {
         a = 0;
         while (a + 1 < A && item >= L.rec_prefix[a + 1]) ++a;
         slot = item - L.rec_prefix[a];
     };
 
+    // The CTA takes one record at a time; its reducing warps split the row's columns among
+    // themselves in chunks of 64 vectors, so even a single record finishes in a few microseconds.
+    const int n_cta = cta < total ? (total - cta + G - 1) / G : 0;
+    constexpr int U = 2, R = 8;
+    const int nchunks = (nvec + 32 * U - 1) / (32 * U);
     if (warp < ND) {
-        const int n_w = count_of(warp);
-        for (int i = 0; i < n_w; ++i) {
-            int a, slot;
-            locate(first_of(warp) + i * stride, a, slot);
+        // The routing words of the next record are fetched while the current one is reduced.
+        auto fetch = [&](int i, int& a, int& slot, int& e, int& pos) {
+            locate(cta + i * G, a, slot);
             const int* meta = reinterpret_cast<const int*>(stage + ((size_t)a * C + slot) * g.rec_bytes + g.meta_off);
-            int row = -1;
+            e = -1;
+            pos = 0;
             if (lane < K) {
-                const int e = __ldcg(meta + lane);
+                e = __ldcg(meta + lane);
+                pos = __ldcg(meta + K + lane);
+            }
+        };
+        int a_n = 0, slot_n = 0, e_n = -1, pos_n = 0;
+        if (n_cta > 0) fetch(0, a_n, slot_n, e_n, pos_n);
+        for (int i = 0; i < n_cta; ++i) {
+            const int a = a_n, slot = slot_n, e = e_n, pos = pos_n;
+            if (i + 1 < n_cta) fetch(i + 1, a_n, slot_n, e_n, pos_n);
+            int row = -1;
+            {
                 const int el = e - fi * EL;
                 if (e >= 0 && el >= 0 && el < EL) {
-                    row = L.row_base[a * EL + el] + __ldcg(meta + K + lane);
+                    row = L.row_base[a * EL + el] + pos;
                     if (row < 0 || row >= rows_cap) row = -1;
                 }
             }
@@ -376,10 +388,10 @@ reply_kernel(const RankCtx c, const FfnWs ws, const unsigned char* __restrict__ 
             if (row >= 0) s_rows[warp][__popc(hits & ptx::lanemask_lt())] = row;
             __syncwarp();
             unsigned char* out = reply + ((size_t)a * C + slot) * g.row_bytes;
-            if (nh == 1) {
-                const unsigned char* src = rows + (size_t)s_rows[warp][0] * g.row_bytes;
-                constexpr int U = 8;
-                for (int v = lane; v < nvec; v += 32 * U) {
+            for (int ch = warp; ch < nchunks; ch += ND) {
+                const int v = ch * 32 * U + lane;
+                if (nh == 1) {
+                    const unsigned char* src = rows + (size_t)s_rows[warp][0] * g.row_bytes;
                     uint4 x[U];
 #pragma unroll
                     for (int u = 0; u < U; ++u)
@@ -387,12 +399,9 @@ reply_kernel(const RankCtx c, const FfnWs ws, const unsigned char* __restrict__ 
 #pragma unroll
                     for (int u = 0; u < U; ++u)
                         if (v + u * 32 < nvec) *reinterpret_cast<uint4*>(out + (size_t)(v + u * 32) * 16) = x[u];
-                }
-            } else {
-                // Rows are fetched eight at a time for two vectors per lane, so sixteen 16-byte
-                // loads are in flight per lane; the additions still happen in top-k order.
-                constexpr int U = 2, R = 8;
-                for (int v = lane; v < nvec; v += 32 * U) {
+                } else {
+                    // Rows are fetched eight at a time for two vectors per lane: sixteen 16-byte loads
+                    // in flight per lane; the additions still happen in top-k order.
                     float acc[U][8];
 #pragma unroll
                     for (int u = 0; u < U; ++u)
@@ -428,26 +437,26 @@ reply_kernel(const RankCtx c, const FfnWs ws, const unsigned char* __restrict__ 
             if (lane == 0) ptx::st_release_cta_shared(&s_done[warp], i + 1);
         }
     } else {
-        // Flag warp: lane w follows reducing warp w; one system-scope fence covers every record
-        // handed over since the last one, so the fence never stalls a reducing warp.
-        const int mine = (lane < ND) ? count_of(lane) : 0;
+        // Flag warp: a record is complete when every reducing warp has handed it over; one
+        // system-scope fence then covers all records completed since the last one.
         int flagged = 0;
         unsigned idle = 0;
         const long long t_begin = clock64();
-        while (true) {
-            const int d = (lane < ND) ? ptx::ld_acquire_cta_shared(&s_done[lane]) : 0;
+        while (flagged < n_cta) {
+            int d = (lane < ND) ? ptx::ld_acquire_cta_shared(&s_done[lane]) : n_cta;
+            d = __reduce_min_sync(ptx::kFullMask, d);
             if (d > flagged) {
                 ptx::fence_acq_rel_sys();
-                for (int j = flagged; j < d; ++j) {
+                for (int j = flagged + lane; j < d; j += 32) {
                     int a, slot;
-                    locate(first_of(lane) + j * stride, a, slot);
+                    locate(cta + j * G, a, slot);
                     uint32_t* flag = reinterpret_cast<uint32_t*>(c.peer[g.ffn + a] + g.a_reply_flag) + (size_t)fi * C + slot;
                     ptx::st_relaxed_sys(flag, ep);
                 }
                 flagged = d;
                 idle = 0;
+                continue;
             }
-            if (__all_sync(ptx::kFullMask, flagged >= mine)) break;
             if (++idle > 1) __nanosleep(64);
             if ((idle & 255u) == 0 && (poisoned(wc) || clock64() - t_begin > 4 * c.budget)) break;
         }

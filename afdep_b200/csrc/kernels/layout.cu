@@ -24,12 +24,26 @@ route_layout_kernel(const long long* __restrict__ ids, int T, int K, int E, int 
     unsigned long long* agg = reinterpret_cast<unsigned long long*>(scratch + kRouteLayoutHeaderBytes);
     const unsigned ep = ptx::ld_acquire_gpu(epoch) + 1u;
     const WaitCtx wc{nullptr, words, budget, 0, /*kernel=*/7};
-    const int EL = E / F;
-    int *tot = nullptr, *lb = nullptr;
-    const RouteLayoutOut lo{route_e, route_pos, tok_slot};
-    const bool ok = route_layout_phase(ids, T, K, E, EL, F, ep, agg, lo, reinterpret_cast<int*>(smem), wc, &tot, &lb);
+    const int ncols = F + E;
+    RouteLayoutJob job;
+    job.ids = ids;
+    job.T = T;
+    job.K = K;
+    job.E = E;
+    job.EL = E / F;
+    job.F = F;
+    job.ep = ep;
+    job.agg = agg;
+    job.out = RouteLayoutOut{route_e, route_pos, tok_slot};
+    job.wh = reinterpret_cast<int*>(smem);
+    job.tot = job.wh + (blockDim.x >> 5) * ncols;
+    job.lb = job.tot + ncols;
+    job.local = nullptr;
+    job.redundant = 0;
+    int* tot = job.tot;
+    int* lb = job.lb;
+    const bool ok = route_layout_phase(job, wc);
     if (blockIdx.x == gridDim.x - 1) {
-        const int ncols = F + E;
         for (int col = threadIdx.x; col < ncols; col += blockDim.x) counts[col] = ok ? lb[col] + tot[col] : -1;
     }
     __syncthreads();

@@ -35,12 +35,26 @@ route_layout_noalloc_kernel(const long long* __restrict__ ids, int T, int K, int
     unsigned long long* agg = reinterpret_cast<unsigned long long*>(scratch + afdep::kRouteLayoutHeaderBytes);
     const unsigned ep = afdep::ptx::ld_acquire_gpu(epoch) + 1u;
     const afdep::WaitCtx wc{nullptr, words, budget, 0, /*kernel=*/8};
-    int *tot = nullptr, *lb = nullptr;
-    const afdep::RouteLayoutOut lo{route_e, route_pos, tok_slot};
-    const bool ok =
-        afdep::route_layout_phase(ids, T, K, E, E / F, F, ep, agg, lo, reinterpret_cast<int*>(smem), wc, &tot, &lb);
+    const int ncols = F + E;
+    afdep::RouteLayoutJob job;
+    job.ids = ids;
+    job.T = T;
+    job.K = K;
+    job.E = E;
+    job.EL = E / F;
+    job.F = F;
+    job.ep = ep;
+    job.agg = agg;
+    job.out = afdep::RouteLayoutOut{route_e, route_pos, tok_slot};
+    job.wh = reinterpret_cast<int*>(smem);
+    job.tot = job.wh + (blockDim.x >> 5) * ncols;
+    job.lb = job.tot + ncols;
+    job.local = nullptr;
+    job.redundant = 0;
+    int* tot = job.tot;
+    int* lb = job.lb;
+    const bool ok = afdep::route_layout_phase(job, wc);
     if (blockIdx.x == gridDim.x - 1) {
-        const int ncols = F + E;
         for (int col = threadIdx.x; col < ncols; col += blockDim.x) counts[col] = ok ? lb[col] + tot[col] : -1;
     }
     __syncthreads();

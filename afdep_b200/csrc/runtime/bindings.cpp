@@ -18,6 +18,7 @@
 #include <memory>
 #include <thread>
 
+#include "afdep/gemm_api.h"
 #include "afdep/kernels.h"
 #include "afdep/route_layout_api.h"
 #include "driver.hpp"
@@ -395,6 +396,83 @@ py::tuple route_layout(const torch::Tensor& ids, int64_t num_experts, int64_t ff
     return py::make_tuple(route_e, route_pos, tok_slot, counts);
 }
 
+namespace {
+
+// Tensor map of a row-major [rows, cols] matrix with 128-byte-swizzled boxes of 128 rows by
+// 128 bytes, the tile shape the grouped GEMM's shared-memory descriptors expect.
+CUtensorMap make_tile_map(const void* base, int64_t rows, int64_t cols, int elem_bytes) {
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * (cuuint64_t)elem_bytes};
+    const cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), 128u};
+    const cuuint32_t estr[2] = {1u, 1u};
+    const CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    drv_check(AFDEP_DRV(cuTensorMapEncodeTiled)(&map, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+                                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE),
+              "cuTensorMapEncodeTiled");
+    return map;
+}
+
+}  // namespace
+
+// out[rows, N or N/2] = A[rows, K] x W[e][N, K]^T per expert segment, on tcgen05.
+// a: bf16 or e4m3 [rows, K]; w: same dtype [experts, N, K]; ends: int32 [experts].
+torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& w, const torch::Tensor& ends, int64_t alignment,
+                           bool swiglu, const c10::optional<torch::Tensor>& row_scale,
+                           const c10::optional<torch::Tensor>& a_scale, const c10::optional<torch::Tensor>& w_scale,
+                           const c10::optional<torch::Tensor>& out_opt, int64_t ctas) {
+    TORCH_CHECK(a.is_cuda() && w.is_cuda() && ends.is_cuda(), "grouped_gemm needs CUDA tensors");
+    TORCH_CHECK(a.dim() == 2 && w.dim() == 3 && a.is_contiguous() && w.is_contiguous(), "a [rows,K], w [experts,N,K], contiguous");
+    TORCH_CHECK(a.scalar_type() == w.scalar_type(), "a and w must have the same dtype");
+    const bool fp8 = a.scalar_type() == torch::kFloat8_e4m3fn;
+    TORCH_CHECK(fp8 || a.scalar_type() == torch::kBFloat16, "bf16 or float8_e4m3fn operands");
+    const int64_t rows = a.size(0), K = a.size(1), E = w.size(0), N = w.size(1);
+    TORCH_CHECK(w.size(2) == K && K % 128 == 0 && N % 128 == 0, "K and N must be multiples of 128");
+    TORCH_CHECK(alignment % 128 == 0, "expert_alignment must be a multiple of 128 for the grouped GEMM");
+    TORCH_CHECK(ends.scalar_type() == torch::kInt32 && ends.numel() == E && E <= kMaxExpertsLocal, "ends: int32 [experts]");
+    TORCH_CHECK(reinterpret_cast<uintptr_t>(a.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(w.data_ptr()) % 16 == 0,
+                "operands must be 16-byte aligned");
+    c10::cuda::CUDAGuard guard(a.device());
+    const int64_t ldc = swiglu ? N / 2 : N;
+    torch::Tensor out = out_opt.has_value()
+                            ? *out_opt
+                            : torch::empty({rows, ldc}, torch::TensorOptions().dtype(torch::kBFloat16).device(a.device()));
+    TORCH_CHECK(out.scalar_type() == torch::kBFloat16 && out.is_contiguous() && out.size(0) == rows && out.size(1) == ldc,
+                "out must be contiguous bf16 [rows, N or N/2]");
+    GroupedGemmArgs g{};
+    g.rows = (int)rows;
+    g.N = (int)N;
+    g.K = (int)K;
+    g.experts = (int)E;
+    g.alignment = (int)alignment;
+    g.ends = ends.data_ptr<int>();
+    g.out = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
+    g.ldc = (int)ldc;
+    g.swiglu = swiglu ? 1 : 0;
+    g.row_scale = row_scale.has_value() ? row_scale->data_ptr<float>() : nullptr;
+    g.fp8 = fp8 ? 1 : 0;
+    if (fp8) {
+        TORCH_CHECK(a_scale.has_value() && w_scale.has_value(), "FP8 operands need a_scale [rows, K/128] and w_scale [experts, N/128, K/128]");
+        TORCH_CHECK(a_scale->scalar_type() == torch::kFloat32 && a_scale->size(0) == rows && a_scale->size(1) == K / 128, "a_scale shape");
+        TORCH_CHECK(w_scale->scalar_type() == torch::kFloat32 && w_scale->is_contiguous() && w_scale->numel() == E * (N / 128) * (K / 128),
+                    "w_scale shape");
+        g.a_scale = a_scale->data_ptr<float>();
+        g.a_scale_s0 = a_scale->stride(0);
+        g.a_scale_s1 = a_scale->stride(1);
+        g.w_scale = w_scale->data_ptr<float>();
+    }
+    if (rows == 0) return out;
+    const int elem = fp8 ? 1 : 2;
+    const CUtensorMap map_a = make_tile_map(a.data_ptr(), rows, K, elem);
+    const CUtensorMap map_w = make_tile_map(w.data_ptr(), E * N, K, elem);
+    int sms = 0;
+    rt_check(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, a.get_device()), "device attribute");
+    const int grid = ctas > 0 ? (int)ctas : sms;
+    rt_check(launch_grouped_gemm(map_a, map_w, g, grid, at::cuda::getCurrentCUDAStream().stream()), "grouped_gemm launch");
+    return out;
+}
+
 }  // namespace afdep
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -402,6 +480,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.doc() = "afdep_b200 native runtime (sm_100a)";
     m.attr("max_ranks") = afdep::kMaxRanks;
     m.def("vmm_supported", [](int device) { return afdep::SymmetricHeap::vmm_supported(device); });
+    m.def("grouped_gemm", &afdep::grouped_gemm, py::arg("a"), py::arg("w"), py::arg("ends"), py::arg("alignment"),
+          py::arg("swiglu") = false, py::arg("row_scale") = py::none(), py::arg("a_scale") = py::none(),
+          py::arg("w_scale") = py::none(), py::arg("out") = py::none(), py::arg("ctas") = 0);
     m.def("route_layout", &afdep::route_layout, py::arg("ids"), py::arg("num_experts"), py::arg("ffn_ranks"));
     py::class_<NativeBuffer>(m, "NativeBuffer")
         .def(py::init<int, int, int, int, int, int, int, bool, int, int, int, int, double, int64_t, const std::string&, bool>(),

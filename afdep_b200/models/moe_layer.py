@@ -1,0 +1,118 @@
+"""An attention-FFN-disaggregated MoE layer on top of `Buffer`: the end-to-end use of the library.
+
+Attention ranks hold tokens and a router decision; FFN ranks hold SwiGLU experts
+(hidden -> intermediate -> hidden).  One layer step is
+
+    attention:  source_dispatch(x, ids, weights)            ...            out = source_collect()
+    FFN:                        worker_receive -> experts on tcgen05 -> worker_reply
+
+The expert path is two grouped GEMMs (`afdep_b200.ops.grouped_gemm`):
+  1. gate|up projection with SwiGLU in the epilogue.  With ``weights="fp8"`` the weights are
+     stored e4m3 with one fp32 scale per 128 x 128 block and multiplied with e4m3 activations
+     carrying per-row, per-128-column scales (block-scaled FP8, promotion in the epilogue);
+  2. down projection in BF16 with the routing weight applied to every output row.
+The down projection keeps its e4m3-rounded weights in BF16: its input is the BF16 SwiGLU
+output, and the tensor cores do not mix BF16 and FP8 operands.
+
+The reference library stops at the exchange (its README leaves routing, quantization and
+expert GEMMs to the caller); this module is the "caller" used by the end-to-end benchmark.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..buffer import Buffer, ReceiveResult
+from ..config import Config
+from ..ops import grouped_gemm as gg
+
+
+@dataclass
+class ExpertWeights:
+    """Weights of the local experts of one FFN rank, in the layouts the kernels consume."""
+
+    w_gate_up: torch.Tensor            # [E, 2I, H] bf16 or e4m3, gate/up interleaved in 64-row blocks
+    w_gate_up_scale: torch.Tensor | None   # [E, 2I/128, H/128] fp32 (FP8 only)
+    w_down: torch.Tensor               # [E, H, I] bf16
+    intermediate: int
+    mode: str
+
+    @staticmethod
+    def random(num_local_experts: int, hidden: int, intermediate: int, *, mode: str = "bf16", seed: int = 0, device="cuda", std: float = 0.02) -> "ExpertWeights":
+        """Random-init N(0, std) experts; ``mode`` is "bf16" or "fp8" (e4m3 storage, 128 x 128 scales)."""
+        assert mode in ("bf16", "fp8")
+        gen = torch.Generator(device=device).manual_seed(seed)
+        E, I, H = num_local_experts, intermediate, hidden
+        gate_up = torch.empty((E, 2 * I, H), device=device, dtype=torch.bfloat16)
+        down = torch.empty((E, H, I), device=device, dtype=torch.bfloat16)
+        for e in range(E):       # expert by expert: the fp32 staging stays small
+            wg = torch.randn((I, H), generator=gen, device=device) * std
+            wu = torch.randn((I, H), generator=gen, device=device) * std
+            gate_up[e] = gg.interleave_gate_up(wg[None], wu[None])[0].to(torch.bfloat16)
+            down[e] = (torch.randn((H, I), generator=gen, device=device) * std).to(torch.bfloat16)
+        if mode == "bf16":
+            return ExpertWeights(gate_up, None, down, I, mode)
+        q = torch.empty((E, 2 * I, H), device=device, dtype=torch.float8_e4m3fn)
+        scale = torch.empty((E, 2 * I // 128, H // 128), device=device, dtype=torch.float32)
+        for e in range(E):
+            qe, se = gg.quantize_weight_blocks_fp8(gate_up[e : e + 1].float())
+            q[e], scale[e] = qe[0], se[0]
+            de, ds = gg.quantize_weight_blocks_fp8(down[e : e + 1].float())
+            blocks = de.float().view(1, H // 128, 128, I // 128, 128) * ds.view(1, H // 128, 1, I // 128, 1)
+            down[e] = blocks.reshape(H, I).to(torch.bfloat16)      # e4m3-rounded values, BF16 storage
+        return ExpertWeights(q, scale, down, I, mode)
+
+
+def run_experts(received: ReceiveResult, weights: ExpertWeights, alignment: int, *, scratch: dict | None = None) -> torch.Tensor:
+    """BF16 rows for ``worker_reply``: SwiGLU MLP of every received row, times its routing weight."""
+    x, ends = received.recv_x, received.recv_count_psum
+    fp8 = weights.mode == "fp8"
+    if fp8 and x.dtype != torch.float8_e4m3fn:
+        # BF16 dispatch into FP8 experts: quantise on the FFN rank (one fused torch pass)
+        x, a_scale = gg.quantize_rows_fp8(x)
+    else:
+        a_scale = received.recv_scale
+    h = gg.grouped_gemm(x, weights.w_gate_up, ends, alignment, swiglu=True, a_scale=a_scale if fp8 else None,
+                        w_scale=weights.w_gate_up_scale)
+    return gg.grouped_gemm(h, weights.w_down, ends, alignment, row_scale=received.recv_topk_weights)
+
+
+def reference_experts(received: ReceiveResult, weights: ExpertWeights, alignment: int) -> torch.Tensor:
+    """The same MLP in fp32 torch on the dequantised operands (test oracle)."""
+    x, ends = received.recv_x, received.recv_count_psum
+    fp8 = weights.mode == "fp8"
+    a_scale = received.recv_scale
+    if fp8 and x.dtype != torch.float8_e4m3fn:
+        x, a_scale = gg.quantize_rows_fp8(x)
+    h = gg.reference_grouped_gemm(x, weights.w_gate_up, ends.cpu(), alignment, swiglu=True, a_scale=a_scale if fp8 else None,
+                                  w_scale=weights.w_gate_up_scale)
+    h = h.to(torch.bfloat16)
+    y = gg.reference_grouped_gemm(h, weights.w_down, ends.cpu(), alignment, row_scale=received.recv_topk_weights)
+    return y.to(torch.bfloat16)
+
+
+class AfdMoELayer:
+    """One MoE layer bound to a Buffer.  Attention ranks call ``forward``, FFN ranks ``serve``."""
+
+    def __init__(self, buffer: Buffer, weights: ExpertWeights | None = None) -> None:
+        self.buffer, self.config = buffer, buffer.config
+        self.weights = weights
+        if buffer.role == "ffn":
+            assert weights is not None, "FFN ranks need expert weights"
+            assert self.config.expert_alignment % 128 == 0, "the grouped GEMM needs expert_alignment to be a multiple of 128"
+
+    def forward(self, x, ids, topk_weights, x_scale=None, *, bucket: int | None = None):
+        """Attention rank: returns BF16 [T, H], each token's weighted expert outputs summed."""
+        bucket = bucket or self.config.capacity_tokens_per_rank
+        self.buffer.source_dispatch(x, ids, topk_weights, x_scale, bucket=bucket)
+        return self.buffer.source_collect()
+
+    def serve(self, *, bucket: int | None = None) -> ReceiveResult:
+        """FFN rank: receive one exchange, run the local experts, reply."""
+        bucket = bucket or self.config.capacity_tokens_per_rank
+        received = self.buffer.worker_receive(bucket=bucket)
+        rows = run_experts(received, self.weights, self.config.expert_alignment)
+        self.buffer.worker_reply(rows, received.receipt)
+        return received

@@ -1,0 +1,88 @@
+"""Grouped expert GEMM on tcgen05 tensor cores, and the plain-torch reference it is tested against.
+
+``grouped_gemm(a, w, ends, alignment, ...)`` multiplies the expert-major rows returned by
+``worker_receive`` with one weight matrix per local expert:
+
+    out[r] = a[r] @ w[e].T        for rows r of expert e's segment
+
+Operands are BF16, or e4m3 with fp32 block scales (``a_scale [rows, K/128]`` per row and 128
+columns, ``w_scale [experts, N/128, K/128]`` per 128 x 128 block).  ``swiglu=True`` expects the
+gate and up projections interleaved in blocks of 64 rows of ``w`` (see ``interleave_gate_up``)
+and returns ``silu(gate) * up`` with ``N/2`` columns; ``row_scale`` multiplies every output
+row (the routing weight).  Rows outside the expert segments are left untouched.
+"""
+
+from __future__ import annotations
+
+import torch
+
+
+def grouped_gemm(a, w, ends, alignment: int, *, swiglu: bool = False, row_scale=None, a_scale=None, w_scale=None, out=None, ctas: int = 0):
+    from .._native import load_native
+
+    return load_native().grouped_gemm(a, w, ends, int(alignment), bool(swiglu), row_scale, a_scale, w_scale, out, int(ctas))
+
+
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """[E, I, K] gate and up -> [E, 2I, K] with alternating 64-row blocks gate, up, gate, up, ..."""
+    E, I, K = w_gate.shape
+    g = w_gate.reshape(E, I // 64, 64, K)
+    u = w_up.reshape(E, I // 64, 64, K)
+    return torch.stack((g, u), dim=2).reshape(E, 2 * I, K).contiguous()
+
+
+def interleave_gate_up_scales(s_gate: torch.Tensor, s_up: torch.Tensor) -> torch.Tensor:
+    """Block scales of the interleaved matrix.  A 128-row block of it holds 64 gate and 64 up
+    rows from the same 128-row block pair, so gate and up must share their 128 x 128 scale:
+    pass matrices quantized with ``quantize_weight_blocks(..., pair=...)`` or use this on
+    per-64-row scales [E, I/64, K/128]."""
+    E, B, Kb = s_gate.shape
+    return torch.maximum(s_gate, s_up).reshape(E, B, Kb).contiguous()
+
+
+def segment_starts(ends: torch.Tensor, alignment: int) -> torch.Tensor:
+    ends = ends.to(torch.int64)
+    prev = torch.cat((ends.new_zeros(1), ends[:-1]))
+    return (prev + alignment - 1) // alignment * alignment
+
+
+def reference_grouped_gemm(a, w, ends, alignment, *, swiglu=False, row_scale=None, a_scale=None, w_scale=None, interleaved=True):
+    """fp32 reference on dequantised operands; returns fp32 [rows, N or N/2], zero outside segments."""
+    rows, K = a.shape
+    E, N, _ = w.shape
+    af = a.float()
+    if a_scale is not None:
+        af = (af.view(rows, K // 128, 128) * a_scale.float()[:, :, None]).reshape(rows, K)
+    wf = w.float()
+    if w_scale is not None:
+        wf = (wf.view(E, N // 128, 128, K // 128, 128) * w_scale.float().view(E, N // 128, 1, K // 128, 1)).reshape(E, N, K)
+    starts = segment_starts(ends, alignment).tolist()
+    out = torch.zeros((rows, N // 2 if swiglu else N), dtype=torch.float32, device=a.device)
+    for e, (s, t) in enumerate(zip(starts, ends.tolist())):
+        if t <= s:
+            continue
+        y = af[s:t] @ wf[e].T
+        if swiglu:
+            y = y.view(t - s, N // 128, 2, 64)
+            y = (torch.nn.functional.silu(y[:, :, 0]) * y[:, :, 1]).reshape(t - s, N // 2)
+        if row_scale is not None:
+            y = y * row_scale[s:t].float()[:, None]
+        out[s:t] = y
+    return out
+
+
+def quantize_rows_fp8(x: torch.Tensor):
+    """e4m3 rows with one fp32 scale per row and 128 columns (amax / 448)."""
+    rows, K = x.shape
+    g = x.float().view(rows, K // 128, 128)
+    scale = g.abs().amax(dim=2).clamp_min(1e-12) / 448.0
+    return (g / scale[:, :, None]).reshape(rows, K).to(torch.float8_e4m3fn), scale
+
+
+def quantize_weight_blocks_fp8(w: torch.Tensor):
+    """e4m3 weights with one fp32 scale per 128 x 128 block: ([E, N, K] e4m3, [E, N/128, K/128])."""
+    E, N, K = w.shape
+    g = w.float().view(E, N // 128, 128, K // 128, 128)
+    scale = g.abs().amax(dim=(2, 4)).clamp_min(1e-12) / 448.0
+    q = (g / scale[:, :, None, :, None]).reshape(E, N, K).to(torch.float8_e4m3fn)
+    return q, scale.contiguous()

@@ -285,7 +285,10 @@ def main() -> None:
         torch.cuda.current_stream().wait_stream(side)
 
     def timed(copy_inputs: bool, steps: int, warmup: int):
-        times, phases = [], []
+        """Device time of each step.  The kernel-only pass enqueues every step back to back (the
+        L2 flush and the cross-rank barrier sit between the event pairs, outside them) and
+        synchronises once; the end-to-end pass waits for each step's result on the host."""
+        pairs = []
         host_result = torch.zeros(1, dtype=torch.float32).pin_memory()
         for i in range(warmup + steps):
             flush.fill_(i & 0xFF)
@@ -300,10 +303,11 @@ def main() -> None:
                     src = out.float().sum().reshape(1) if out is not None else state[0]["psum"].float().sum().reshape(1)
                     host_result.copy_(src, non_blocking=True)
             e1.record()
-            e1.synchronize()
-            if i >= warmup:
-                times.append(e0.elapsed_time(e1))
-        return times
+            if copy_inputs:
+                e1.synchronize()
+            pairs.append((e0, e1))
+        torch.cuda.synchronize()
+        return [a.elapsed_time(b) for a, b in pairs[warmup:]]
 
     torch.cuda.synchronize()
     if multi:
