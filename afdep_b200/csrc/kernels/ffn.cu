@@ -353,15 +353,22 @@ reply_kernel(const RankCtx c, const FfnWs ws, const unsigned char* __restrict__ 
         slot = item - L.rec_prefix[a];
     };
 
-    // The CTA takes one record at a time; its reducing warps split the row's columns among
-    // themselves in chunks of 64 vectors, so even a single record finishes in a few microseconds.
-    const int n_cta = cta < total ? (total - cta + G - 1) / G : 0;
+    // Two ways to spread records over the reducing warps, chosen from the live record count:
+    //   many records: one warp per record (best throughput, a warp streams a whole row);
+    //   few records:  the CTA's warps split one record's columns in chunks of 64 vectors, so a
+    //                 decode-sized exchange finishes in a few microseconds instead of a row time.
     constexpr int U = 2, R = 8;
     const int nchunks = (nvec + 32 * U - 1) / (32 * U);
+    const bool coop = total * 2 < G * ND;
+    const int first = coop ? cta : cta * ND + warp;
+    const int stride = coop ? G : G * ND;
+    auto count_from = [&](int f0) { return f0 < total ? (total - f0 + stride - 1) / stride : 0; };
     if (warp < ND) {
+        const int n_w = count_from(first);
+        const int ch0 = coop ? warp : 0, chs = coop ? ND : 1;
         // The routing words of the next record are fetched while the current one is reduced.
         auto fetch = [&](int i, int& a, int& slot, int& e, int& pos) {
-            locate(cta + i * G, a, slot);
+            locate(first + i * stride, a, slot);
             const int* meta = reinterpret_cast<const int*>(stage + ((size_t)a * C + slot) * g.rec_bytes + g.meta_off);
             e = -1;
             pos = 0;
@@ -371,10 +378,10 @@ reply_kernel(const RankCtx c, const FfnWs ws, const unsigned char* __restrict__ 
             }
         };
         int a_n = 0, slot_n = 0, e_n = -1, pos_n = 0;
-        if (n_cta > 0) fetch(0, a_n, slot_n, e_n, pos_n);
-        for (int i = 0; i < n_cta; ++i) {
+        if (n_w > 0) fetch(0, a_n, slot_n, e_n, pos_n);
+        for (int i = 0; i < n_w; ++i) {
             const int a = a_n, slot = slot_n, e = e_n, pos = pos_n;
-            if (i + 1 < n_cta) fetch(i + 1, a_n, slot_n, e_n, pos_n);
+            if (i + 1 < n_w) fetch(i + 1, a_n, slot_n, e_n, pos_n);
             int row = -1;
             {
                 const int el = e - fi * EL;
@@ -388,7 +395,7 @@ reply_kernel(const RankCtx c, const FfnWs ws, const unsigned char* __restrict__ 
             if (row >= 0) s_rows[warp][__popc(hits & ptx::lanemask_lt())] = row;
             __syncwarp();
             unsigned char* out = reply + ((size_t)a * C + slot) * g.row_bytes;
-            for (int ch = warp; ch < nchunks; ch += ND) {
+            for (int ch = ch0; ch < nchunks; ch += chs) {
                 const int v = ch * 32 * U + lane;
                 if (nh == 1) {
                     const unsigned char* src = rows + (size_t)s_rows[warp][0] * g.row_bytes;
@@ -437,26 +444,28 @@ reply_kernel(const RankCtx c, const FfnWs ws, const unsigned char* __restrict__ 
             if (lane == 0) ptx::st_release_cta_shared(&s_done[warp], i + 1);
         }
     } else {
-        // Flag warp: a record is complete when every reducing warp has handed it over; one
-        // system-scope fence then covers all records completed since the last one.
+        // Flag warp: one system-scope fence covers every record handed over since the last one,
+        // so the fence never stalls a reducing warp.  Cooperative mode: a record is complete when
+        // every warp has handed it over, lanes share the flags; otherwise lane w follows warp w.
+        const int mine = coop ? count_from(cta) : ((lane < ND) ? count_from(cta * ND + lane) : 0);
         int flagged = 0;
         unsigned idle = 0;
         const long long t_begin = clock64();
-        while (flagged < n_cta) {
-            int d = (lane < ND) ? ptx::ld_acquire_cta_shared(&s_done[lane]) : n_cta;
-            d = __reduce_min_sync(ptx::kFullMask, d);
+        while (true) {
+            int d = (lane < ND) ? ptx::ld_acquire_cta_shared(&s_done[lane]) : (coop ? mine : 0);
+            if (coop) d = __reduce_min_sync(ptx::kFullMask, d);
             if (d > flagged) {
                 ptx::fence_acq_rel_sys();
-                for (int j = flagged + lane; j < d; j += 32) {
+                for (int j = coop ? flagged + lane : flagged; j < d; j += coop ? 32 : 1) {
                     int a, slot;
-                    locate(cta + j * G, a, slot);
+                    locate((coop ? cta : cta * ND + lane) + j * stride, a, slot);
                     uint32_t* flag = reinterpret_cast<uint32_t*>(c.peer[g.ffn + a] + g.a_reply_flag) + (size_t)fi * C + slot;
                     ptx::st_relaxed_sys(flag, ep);
                 }
                 flagged = d;
                 idle = 0;
-                continue;
             }
+            if (__all_sync(ptx::kFullMask, flagged >= mine)) break;
             if (++idle > 1) __nanosleep(64);
             if ((idle & 255u) == 0 && (poisoned(wc) || clock64() - t_begin > 4 * c.budget)) break;
         }

@@ -37,6 +37,8 @@ CONFIGS = {
     "2": dict(hidden=4096, experts_per_ffn=64, top_k=8, tokens=2048, payload="bf16", zipf=None),
     "3": dict(hidden=7168, experts_per_ffn=64, top_k=8, tokens=4096, payload="fp8", zipf=1.1),
     "4": dict(hidden=7168, experts_per_ffn=128, top_k=8, tokens=128, payload="bf16", zipf=None),
+    # end-to-end MoE layer: the FFN ranks run SwiGLU experts 7168 -> 2048 -> 7168 on tcgen05
+    "5": dict(hidden=7168, experts_per_ffn=64, top_k=8, tokens=2048, payload="fp8", zipf=None, intermediate=2048),
 }
 
 
@@ -47,6 +49,7 @@ def parse_args():
     p.add_argument("--warmup", type=int, default=5)
     p.add_argument("--impl", choices=("ours", "nccl", "reference"), default="ours")
     p.add_argument("--config", choices=tuple(CONFIGS), default="weak")
+    p.add_argument("--expert-weights", choices=("fp8", "bf16"), default="fp8", help="config 5: storage of the expert weights")
     p.add_argument("--tokens", type=int, default=0, help="override tokens per attention rank")
     p.add_argument("--num-sms", type=int, default=0)
     p.add_argument("--graph", action="store_true", help="replay each step from a CUDA graph")
@@ -207,6 +210,12 @@ def main() -> None:
             s["host"] = [t.pin_memory() if t is not None else None for t in (x, ids, w, scale)]
             s["dev"] = [t.to(dev) if t is not None else None for t in s["host"]]
             s["ids_cpu"] = ids
+        elif "intermediate" in spec:
+            from afdep_b200.models.moe_layer import ExpertWeights
+
+            s["weights"] = ExpertWeights.random(
+                cfg.experts_per_rank, cfg.hidden_size, spec["intermediate"], mode=args.expert_weights, seed=7 + buf.role_rank, device=dev
+            )
         else:
             s["rows"] = torch.zeros((cfg.receive_rows(T), cfg.hidden_size), dtype=torch.bfloat16, device=dev)
         state.append(s)
@@ -234,7 +243,7 @@ def main() -> None:
         if multi:
             buffers[0]._t._nb.barrier() if args.impl == "ours" else dist.barrier()
 
-    phase_log: dict[str, list] = {"dispatch": [], "receive": [], "reply": [], "collect": []}
+    phase_log: dict[str, list] = {"dispatch": [], "receive": [], "experts": [], "reply": [], "collect": []}
 
     def mark(name, fn, record):
         if not record:
@@ -260,7 +269,12 @@ def main() -> None:
         for s in ordered:
             if s["buf"].role == "ffn":
                 rec = mark("receive", lambda: s["buf"].worker_receive(bucket=T), record)
-                rows = rec.recv_x if not cfg.is_fp8 else s["rows"]
+                if "weights" in s:
+                    from afdep_b200.models.moe_layer import run_experts
+
+                    rows = mark("experts", lambda: run_experts(rec, s["weights"], cfg.expert_alignment), record)
+                else:
+                    rows = rec.recv_x if not cfg.is_fp8 else s["rows"]
                 s["psum"] = rec.recv_count_psum
                 mark("reply", lambda: s["buf"].worker_reply(rows, rec.receipt), record)
         for s in ordered:
@@ -385,6 +399,11 @@ def main() -> None:
             "tokens_per_s": round(T * attn / (ms_per_step * 1e-3), 1),
             "per_attention_rank_GBs": round(value / attn, 3),
         },
+        "expert_tflops": (
+            round(6.0 * T * attn * cfg.top_k * cfg.hidden_size * spec["intermediate"] / (ms_per_step * 1e-3) / 1e12, 2)
+            if "intermediate" in spec
+            else None
+        ),
         "phases": phases,
         "clocks": clocks,
         "gpu_launches": launches,
