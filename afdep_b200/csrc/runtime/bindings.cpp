@@ -18,6 +18,7 @@
 #include <memory>
 #include <thread>
 
+#include "afdep/aux_api.h"
 #include "afdep/gemm_api.h"
 #include "afdep/kernels.h"
 #include "afdep/route_layout_api.h"
@@ -308,6 +309,55 @@ public:
         return v;
     }
 
+    // ---- secondary primitives on the auxiliary region ----------------------------------------
+    int64_t aux_data_bytes() const { return geo_.aux_bytes > (size_t)kAuxSignalBytes ? (int64_t)(geo_.aux_bytes - kAuxSignalBytes) : 0; }
+    int64_t aux_slot_bytes() const { return aux_data_bytes() / geo_.world / 16 * 16; }
+
+    // View of this rank's auxiliary data area as bytes (peers write into it).
+    torch::Tensor aux_view() {
+        live();
+        auto* base = static_cast<unsigned char*>(heap_->local()) + geo_.aux_off + kAuxSignalBytes;
+        return torch::from_blob(base, {aux_data_bytes()}, torch::TensorOptions().dtype(torch::kUInt8).device(torch::kCUDA, device_));
+    }
+    void allgather_push(const torch::Tensor& t) {
+        live();
+        const size_t bytes = check_aux_tensor(t);
+        rt_check(launch_allgather_push(ctx_, aux_seq(), t.data_ptr(), bytes, (size_t)aux_slot_bytes(), aux_ctas(bytes), stream()), "all-gather launch");
+        ++launches_;
+    }
+    void allgather_wait() {
+        live();
+        rt_check(launch_allgather_wait(ctx_, aux_seq(), stream()), "all-gather wait launch");
+        ++launches_;
+    }
+    void p2p_send(const torch::Tensor& t, int dst) {
+        live();
+        check_peer(dst);
+        const size_t bytes = check_aux_tensor(t);
+        rt_check(launch_p2p_send(ctx_, aux_seq(), dst, t.data_ptr(), bytes, (size_t)aux_slot_bytes(), aux_ctas(bytes), stream()), "send launch");
+        ++launches_;
+    }
+    void p2p_recv(torch::Tensor& t, int src) {
+        live();
+        check_peer(src);
+        const size_t bytes = check_aux_tensor(t);
+        rt_check(launch_p2p_recv(ctx_, aux_seq(), src, t.data_ptr(), bytes, (size_t)aux_slot_bytes(), aux_ctas(bytes), stream()), "recv launch");
+        ++launches_;
+    }
+    torch::Tensor fetch_rows(const torch::Tensor& idx, int64_t rows_per_rank, int64_t row_bytes) {
+        live();
+        TORCH_CHECK(idx.is_cuda() && idx.scalar_type() == torch::kInt64 && idx.is_contiguous(), "idx: contiguous CUDA int64");
+        TORCH_CHECK(row_bytes % 16 == 0 && rows_per_rank > 0 && rows_per_rank * row_bytes <= aux_data_bytes(), "table shard does not fit the auxiliary region");
+        const int64_t n = idx.numel();
+        auto out = torch::empty({n, row_bytes}, torch::TensorOptions().dtype(torch::kUInt8).device(torch::kCUDA, device_));
+        if (n == 0) return out;
+        const int ctas = (int)std::min<int64_t>(num_sms_, (n + 7) / 8);
+        rt_check(launch_fetch_rows(ctx_, reinterpret_cast<const long long*>(idx.data_ptr<int64_t>()), (int)n, (int)rows_per_rank,
+                                   (int)row_bytes, out.data_ptr(), ctas, stream()), "fetch launch");
+        ++launches_;
+        return out;
+    }
+
     // Per-CTA time stamps of the exchange kernels: int64 [4 kernels][kTraceCtas][4] in
     // nanoseconds of the GPU's global timer; pass enable=false to switch tracing off again.
     torch::Tensor trace(bool enable) {
@@ -341,6 +391,27 @@ public:
     }
 
 private:
+    AuxSeq aux_seq() {
+        int* fl = flags_.data_ptr<int>();
+        AuxSeq q{};
+        q.gather = reinterpret_cast<unsigned*>(fl + 32);
+        q.sent = reinterpret_cast<unsigned*>(fl + 40);
+        q.received = reinterpret_cast<unsigned*>(fl + 48);
+        q.ticket = reinterpret_cast<unsigned*>(fl + 56);
+        return q;
+    }
+    size_t check_aux_tensor(const torch::Tensor& t) const {
+        TORCH_CHECK(t.is_cuda() && t.is_contiguous(), "tensor must be a contiguous CUDA tensor");
+        const size_t bytes = (size_t)t.numel() * t.element_size();
+        TORCH_CHECK(bytes % 16 == 0 && reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0, "tensor must be 16-byte aligned and sized");
+        TORCH_CHECK((int64_t)bytes <= aux_slot_bytes(), "tensor larger than the per-peer slot of the auxiliary region (raise aux_bytes)");
+        return bytes;
+    }
+    int aux_ctas(size_t bytes) const {
+        const int want = (int)((bytes + 65535) / 65536);
+        return want < 1 ? 1 : (want > num_sms_ ? num_sms_ : want);
+    }
+
     static constexpr size_t kHostBlockBytes = 8192;
     static constexpr size_t kHostCountsOff = 1024;
 
@@ -508,6 +579,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("clear_status", &NativeBuffer::clear_status)
         .def("bad_routes", &NativeBuffer::bad_routes)
         .def("trace", &NativeBuffer::trace)
+        .def("aux_data_bytes", &NativeBuffer::aux_data_bytes)
+        .def("aux_slot_bytes", &NativeBuffer::aux_slot_bytes)
+        .def("aux_view", &NativeBuffer::aux_view)
+        .def("allgather_push", &NativeBuffer::allgather_push)
+        .def("allgather_wait", &NativeBuffer::allgather_wait)
+        .def("p2p_send", &NativeBuffer::p2p_send)
+        .def("p2p_recv", &NativeBuffer::p2p_recv)
+        .def("fetch_rows", &NativeBuffer::fetch_rows)
         .def("launches", &NativeBuffer::launches)
         .def("resolved_num_sms", &NativeBuffer::resolved_num_sms)
         .def("device_sms", &NativeBuffer::device_sms)

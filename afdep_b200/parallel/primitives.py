@@ -1,0 +1,83 @@
+"""Secondary primitives on a native Buffer's symmetric heap: all-gather, neighbour send/recv
+with credits, and remote row fetch.  NVLink only.
+
+They live in the heap's auxiliary region, whose size is chosen when the Buffer is built
+(``Buffer(..., aux_bytes=...)``); each rank's data area holds one slot per peer.  The
+reference inherits comparable calls from its vendored transport (pipeline send/recv, an
+in-session all-gather and an embedding-row fetch, csrc/elastic/buffer.hpp:201-474) without
+exposing them in its role API; here they are a thin, explicit layer next to the role API.
+
+Every wait is bounded like the role calls': a peer that never shows up surfaces as
+``AfdepTimeoutError`` at the next ``Buffer.check()``.
+"""
+
+from __future__ import annotations
+
+import torch
+
+
+class HeapPrimitives:
+    def __init__(self, buffer) -> None:
+        if buffer.backend != "native":
+            raise ValueError("heap primitives need the native transport")
+        self._buffer = buffer
+        self._nb = buffer._t._nb
+        self.world_size = buffer.config.world_size
+        self.rank = buffer.rank
+        if self._nb.aux_slot_bytes() <= 0:
+            raise ValueError("build the Buffer with aux_bytes > 0 to use heap primitives")
+
+    @property
+    def slot_bytes(self) -> int:
+        """Largest message / gathered tensor per rank."""
+        return int(self._nb.aux_slot_bytes())
+
+    # ---- all-gather ---------------------------------------------------------------------
+    def all_gather_start(self, tensor: torch.Tensor):
+        """Push ``tensor`` into every peer's slot for this rank.  Returns a handle whose
+        ``wait()`` yields the ``[world_size, *tensor.shape]`` view of the gathered data."""
+        self._nb.allgather_push(tensor)
+        return _GatherHandle(self, tensor.shape, tensor.dtype, tensor.numel() * tensor.element_size())
+
+    def all_gather(self, tensor: torch.Tensor) -> torch.Tensor:
+        return self.all_gather_start(tensor).wait()
+
+    # ---- neighbour send / recv -------------------------------------------------------------
+    def send(self, tensor: torch.Tensor, dst: int) -> None:
+        """One message to ``dst``; waits (on the device) until ``dst`` consumed the previous one."""
+        self._nb.p2p_send(tensor, int(dst))
+
+    def recv(self, out: torch.Tensor, src: int) -> torch.Tensor:
+        """Next message from ``src`` into ``out``; returns the credit to the sender."""
+        self._nb.p2p_recv(out, int(src))
+        return out
+
+    # ---- remote row fetch ---------------------------------------------------------------------
+    def table_shard(self, rows_per_rank: int, row_elems: int, dtype: torch.dtype) -> torch.Tensor:
+        """This rank's shard ``[rows_per_rank, row_elems]`` of a table spread over all ranks,
+        as a view of the auxiliary data area.  Fill it, then ``Buffer``-barrier before fetching."""
+        n = rows_per_rank * row_elems * torch.empty((), dtype=dtype).element_size()
+        return self._nb.aux_view()[:n].view(dtype).view(rows_per_rank, row_elems)
+
+    def fetch_rows(self, idx: torch.Tensor, rows_per_rank: int, row_elems: int, dtype: torch.dtype) -> torch.Tensor:
+        """Rows ``idx`` (global row numbers, owner = idx // rows_per_rank) gathered over NVLink."""
+        row_bytes = row_elems * torch.empty((), dtype=dtype).element_size()
+        raw = self._nb.fetch_rows(idx, int(rows_per_rank), int(row_bytes))
+        return raw.view(dtype).view(idx.numel(), row_elems)
+
+    def barrier(self) -> None:
+        """Device-side barrier over all ranks on the current stream."""
+        self._nb.barrier()
+
+
+class _GatherHandle:
+    def __init__(self, owner: HeapPrimitives, shape, dtype, nbytes: int) -> None:
+        self._owner, self._shape, self._dtype, self._nbytes = owner, tuple(shape), dtype, nbytes
+
+    def wait(self) -> torch.Tensor:
+        o = self._owner
+        o._nb.allgather_wait()
+        view = o._nb.aux_view()
+        slot = o.slot_bytes
+        rows = view[: o.world_size * slot].view(o.world_size, slot)[:, : self._nbytes]
+        return rows.view(self._dtype).view(o.world_size, *self._shape) if rows.is_contiguous() else rows.contiguous().view(self._dtype).view(o.world_size, *self._shape)
