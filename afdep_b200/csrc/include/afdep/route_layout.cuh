@@ -11,7 +11,8 @@
 //
 // Two ways to split the work:
 //   distributed  every CTA owns a contiguous chunk of tokens; warps rank inside their
-//                sub-range (match-any), a shared-memory scan joins the warps, a decoupled
+//                sub-range (shuffle compares inside a token, one token at a time on the
+//                warp's counters), a shared-memory scan joins the warps, a decoupled
 //                look-back over epoch-tagged aggregates in global scratch joins the CTAs.
 //   redundant    for small inputs every CTA ranks ALL tokens itself and keeps the part it
 //                owns: no traffic between CTAs at all, which is what decode-sized batches want.

@@ -1,21 +1,20 @@
 // Attention-side dispatch: route guard, deterministic layout and payload push in ONE launch.
 //
-// Phase 1 (layout) — every CTA owns a contiguous chunk of tokens.  Its warps rank each
-// (token, k) choice among the earlier choices of the same expert and each (token, FFN rank)
-// record among the earlier records for that rank, first inside the warp's sub-range, then
-// across warps (shared-memory scan), then across CTAs (decoupled look-back over epoch-tagged
-// aggregates in global memory).  The result is a placement that depends only on the inputs:
-// record slot = number of earlier tokens of this source that also go to that FFN rank, and
-// pos = number of earlier choices of that expert by this source.  The last CTA ends up with
-// the source's totals and pushes them to the FFN ranks (the count "all-to-all") before any
-// payload leaves.
+// Phase 1 (layout, route_layout.cuh) ranks every (token, k) choice among the earlier choices
+// of the same expert and every (token, FFN rank) record among the earlier records for that
+// rank, so placement depends only on the inputs.  Large batches split the tokens over the
+// CTAs and join them with a decoupled look-back; decode-sized batches let every CTA rank all
+// tokens itself, with no traffic between CTAs.  The CTA's part of the table stays in shared
+// memory for phase 2.  The CTA that holds the source's totals pushes them to the FFN ranks
+// (the count "all-to-all") from its flag warp, ahead of the payload flags.
 //
-// Phase 2 (push) — one warp per token: a bulk async copy brings the row into shared memory
-// once, lanes append scales/routes/weights, and one bulk store per destination FFN rank
-// writes the finished record straight into that rank's staging slot over NVLink.  Once a
-// store group has completed, the data warp hands the token to the CTA's flag warp, which
-// issues the system-scope fence and the 4-byte arrival flag per record; the receiver can
-// start on a record as soon as it has landed, and the (slow) fence never stalls a data warp.
+// Phase 2 (push) — one data warp per token over a ring of record buffers: a bulk async copy
+// brings the row into shared memory once, lanes append scales/routes/weights, and one bulk
+// store per destination FFN rank writes the finished record straight into that rank's staging
+// slot over NVLink.  Once a store group has completed, the data warp hands the token to the
+// CTA's flag warp, which issues the system-scope fence and the 4-byte arrival flag per record;
+// the receiver can start on a record as soon as it has landed, and the (slow) fence never
+// stalls a data warp.
 //
 // Replaces, for the AFD case, the reference's dispatch_impl (notify + dispatch warps,
 // deep_ep/include/deep_ep/impls/dispatch.cuh:18-433), its deterministic prologue

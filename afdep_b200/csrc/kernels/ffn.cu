@@ -128,6 +128,37 @@ __device__ void load_layout(const RankCtx& c, const FfnWs& ws, LayoutSmem& L) {
     __syncthreads();
 }
 
+
+// Dense work index -> (source, slot), ordered by slot first and source second, so that the
+// records of all sources advance together: every attention rank starts seeing its rows (and
+// its reply flags) from the beginning of the kernel instead of one source after the other.
+__device__ __forceinline__ void locate_striped(const LayoutSmem& L, int A, int j, int& a, int& slot) {
+    // cum(s) = number of records with slot < s = sum over sources of min(count, s)
+    int lo = 0, hi = 1;
+    for (int q = 0; q < A; ++q) hi = max(hi, L.rec_prefix[q + 1] - L.rec_prefix[q]);
+    // largest s with cum(s) <= j
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        int cum = 0;
+        for (int q = 0; q < A; ++q) cum += min(L.rec_prefix[q + 1] - L.rec_prefix[q], mid);
+        if (cum <= j) lo = mid; else hi = mid;
+    }
+    int cum = 0;
+    for (int q = 0; q < A; ++q) cum += min(L.rec_prefix[q + 1] - L.rec_prefix[q], lo);
+    int r = j - cum;            // r-th source (in rank order) that still has a record at this slot
+    slot = lo;
+    a = 0;
+    for (int q = 0; q < A; ++q) {
+        if (L.rec_prefix[q + 1] - L.rec_prefix[q] > lo) {
+            if (r == 0) {
+                a = q;
+                break;
+            }
+            --r;
+        }
+    }
+}
+
 // Stand-alone layout pass, used when the host wants exact counts before it allocates the
 // receive tensors.  Writes aligned per-expert counts and a sequence number to mapped host
 // memory; the receive kernel that follows is launched with layout_ready = 1.
@@ -197,12 +228,7 @@ receive_kernel(const RankCtx c, const FfnWs ws, const ReceiveArgs r) {
     const int first = cta * NW + warp, stride = G * NW;
     const int n_w = first < total ? (total - first + stride - 1) / stride : 0;
 
-    auto locate = [&](int i, int& a, int& slot) {
-        const int item = first + i * stride;
-        a = 0;
-        while (a + 1 < A && item >= L.rec_prefix[a + 1]) ++a;
-        slot = item - L.rec_prefix[a];
-    };
+    auto locate = [&](int i, int& a, int& slot) { locate_striped(L, A, first + i * stride, a, slot); };
     // Start pulling record i into its ring buffer.  Non-blocking mode gives up at once when the
     // record has not arrived; blocking mode spins (bounded).  Returns 1 issued, 0 not yet, -1 dead.
     auto issue = [&](int i, bool blocking) -> int {
@@ -347,11 +373,7 @@ reply_kernel(const RankCtx c, const FfnWs ws, const unsigned char* __restrict__ 
     unsigned char* reply = heap + g.f_reply;
     const int total = dead ? 0 : L.rec_prefix[A];
     const int nvec = g.hidden / 8;    // 16-byte vectors per row
-    auto locate = [&](int item, int& a, int& slot) {
-        a = 0;
-        while (a + 1 < A && item >= L.rec_prefix[a + 1]) ++a;
-        slot = item - L.rec_prefix[a];
-    };
+    auto locate = [&](int item, int& a, int& slot) { locate_striped(L, A, item, a, slot); };
 
     // Two ways to spread records over the reducing warps, chosen from the live record count:
     //   many records: one warp per record (best throughput, a warp streams a whole row);
