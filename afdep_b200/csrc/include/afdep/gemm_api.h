@@ -16,7 +16,7 @@ struct GroupedGemmArgs {
     const int* ends;     // device [experts]: end row of each expert segment (recv_count_psum)
     __nv_bfloat16* out;  // [rows, ldc]
     int ldc;             // N, or N / 2 with swiglu
-    int swiglu;          // 1: tile columns [0,64) are gate, [64,128) up; out = silu(gate) * up
+    int swiglu;          // 1: W rows alternate 32 gate / 32 up; out = silu(gate) * up with N/2 columns
     const float* row_scale;   // optional [rows]: routing weight applied to the output row
     int fp8;             // 1: A and W are e4m3 with the scales below
     const float* a_scale;     // element (row, kb) at a_scale[row * s0 + kb * s1]

@@ -36,6 +36,7 @@ struct AttnWs {
     unsigned* epoch;    // [0] dispatch, [1] collect: exchanges completed so far
     unsigned* ticket;   // [0] dispatch, [1] collect: CTAs that reached the end of the launch
     unsigned long long* agg;   // [max_ctas][ffn + num_experts]: (epoch << 32 | count)
+    unsigned* chunk_done;      // [max_ctas]: epoch at which that CTA's chunk of the layout became final
     int* route_e;       // [capacity][top_k] expert or -1
     int* route_pos;     // [capacity][top_k] rank of the choice within (source, expert)
     int* tok_slot;      // [capacity][ffn] record slot on that FFN rank or -1
@@ -58,6 +59,10 @@ struct DispatchArgs {
     const long long* ids;   // [T][top_k] int64
     const float* weights;   // [T][top_k]
     int T;
+    // 0: arrival flags are released by the CTA's flag warp behind a system-scope fence.
+    // 1: experimental, AFDEP_FLAG_MODE=1: the data warp that saw its bulk stores complete
+    //    releases the flags itself with relaxed system-scope stores and no fence.
+    int flag_mode;
 };
 
 struct ReceiveArgs {

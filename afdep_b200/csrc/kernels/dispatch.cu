@@ -82,13 +82,21 @@ dispatch_kernel(const RankCtx c, const AttnWs ws, const DispatchArgs a, const Di
     job.F = F;
     job.ep = ep;
     job.agg = ws.agg;
-    job.out = RouteLayoutOut{local ? nullptr : ws.route_e, local ? nullptr : ws.route_pos, ws.tok_slot};
+    job.out = RouteLayoutOut{plan.redundant ? nullptr : ws.route_e, plan.redundant ? nullptr : ws.route_pos, ws.tok_slot};
     job.wh = reinterpret_cast<int*>(overlay);
     job.tot = tot;
     job.lb = lb;
     job.local = local;
     job.redundant = plan.redundant;
     const bool alive = route_layout_phase(job, wc);
+    // Phase 2 walks the tokens round-robin over all CTAs (so records reach the receivers in
+    // slot order).  When the layout is distributed, a token's routing words were produced by
+    // the CTA that owns its chunk: publish "my chunk is final" for the others to wait on.
+    if (!plan.redundant) {
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) ptx::st_release_gpu(&ws.chunk_done[cta], alive ? ep : 0u);
+    }
     // Shared memory changes hands from generic-proxy scratch to bulk-copy buffers.
     ptx::fence_proxy_async_smem();
 
@@ -108,18 +116,48 @@ dispatch_kernel(const RankCtx c, const AttnWs ws, const DispatchArgs a, const Di
 
     const unsigned char* xb = static_cast<const unsigned char*>(a.x);
     const int sg = g.fp8 ? g.scale_groups : 0;
-    auto tokens_of = [&](int w) { return (alive && t0 + w < t1) ? (t1 - (t0 + w) + ND - 1) / ND : 0; };
-    auto local_row = [&](int t) { return local + (size_t)(plan.redundant ? t : t - t0) * LW; };
-    auto slot_of = [&](int t, int f) { return local ? local_row(t)[2 * K + f] : ws.tok_slot[(size_t)t * F + f]; };
+    // Token j of data warp w in this CTA: consecutive tokens go to consecutive warps of
+    // consecutive CTAs, so the whole grid sweeps the batch front to back.
+    const int tok_stride = G * ND;
+    auto token_of = [&](int w, int j) { return (j * G + cta) * ND + w; };
+    auto tokens_of = [&](int w) { return (alive && token_of(w, 0) < T) ? (T - token_of(w, 0) + tok_stride - 1) / tok_stride : 0; };
+    const bool use_local = plan.redundant != 0;      // the shared-memory table covers every token
+    const int chunk = (T + G - 1) / G;
+    auto local_row = [&](int t) { return local + (size_t)t * LW; };
+    auto slot_of = [&](int t, int f) { return use_local ? local_row(t)[2 * K + f] : ws.tok_slot[(size_t)t * F + f]; };
 
     if (warp < ND) {
-        const int first = t0 + warp;
         const int n_w = tokens_of(warp);
         unsigned phase_bits = 0;      // lane 0: parity of each buffer's mbarrier
+        int ready_upto = use_local ? G : 0;          // chunks [0, ready_upto) are known to be final
+        bool ok = true;
 
         // A(i): start loading token i into its ring buffer and append its metadata.
         auto stage = [&](int i, int& slot, unsigned& mask) {
-            const int t = first + i * ND;
+            const int t = token_of(warp, i);
+            const int owner = t / chunk;
+            if (owner >= ready_upto) {               // warp-uniform: wait for the owner's layout
+                bool fin = true;
+                if (lane == 0) {
+                    unsigned seen = 0;
+                    fin = spin_until(wc, [&] {
+                        seen = ptx::ld_acquire_gpu(&ws.chunk_done[owner]);
+                        return seen == ep;
+                    });
+                    if (!fin) {
+                        report(wc, kTimeoutLookback, owner, ep, ep, seen, cta, 2);
+                        poison(wc);
+                    }
+                }
+                fin = __shfl_sync(ptx::kFullMask, fin, 0);
+                if (!fin) {
+                    ok = false;
+                    slot = -1;
+                    mask = 0;
+                    return;
+                }
+                ready_upto = owner + 1;
+            }
             slot = (lane < F) ? slot_of(t, lane) : -1;
             mask = __ballot_sync(ptx::kFullMask, slot >= 0);
             if (mask == 0) return;
@@ -131,7 +169,7 @@ dispatch_kernel(const RankCtx c, const AttnWs ws, const DispatchArgs a, const Di
             }
             int* meta = reinterpret_cast<int*>(buf + g.meta_off);
             if (lane < K) {
-                if (local) {
+                if (use_local) {
                     const int* row = local_row(t);
                     meta[lane] = row[lane];
                     meta[K + lane] = row[K + lane];
@@ -149,9 +187,8 @@ dispatch_kernel(const RankCtx c, const AttnWs ws, const DispatchArgs a, const Di
 
         int slot_c = -1, slot_n = -1;
         unsigned mask_c = 0, mask_n = 0;
-        bool ok = true;
         if (n_w > 0) stage(0, slot_c, mask_c);
-        for (int i = 0; i < n_w; ++i) {
+        for (int i = 0; i < n_w && ok; ++i) {
             // Buffer (i+1) % NB last held token i+1-NB, whose stores completed at step i-1.
             if (i + 1 < n_w) stage(i + 1, slot_n, mask_n);
             __syncwarp();
@@ -167,7 +204,7 @@ dispatch_kernel(const RankCtx c, const AttnWs ws, const DispatchArgs a, const Di
                 }
                 ok = __shfl_sync(ptx::kFullMask, ok, 0);
                 if (!ok) break;
-                const int t = first + i * ND;
+                const int t = token_of(warp, i);
                 for (unsigned m = mask_c; m; m &= m - 1) {
                     const int f = __ffs(m) - 1;
                     const int s = __shfl_sync(ptx::kFullMask, slot_c, f);
@@ -184,6 +221,15 @@ dispatch_kernel(const RankCtx c, const AttnWs ws, const DispatchArgs a, const Di
                 ptx::bulk_commit();            // one group per token, possibly empty
                 if (i >= L) {
                     ptx::bulk_wait<L>();       // token i-L has fully landed at its destinations
+                    if (a.flag_mode == 1) {
+                        ptx::fence_proxy_async_global();
+                        const int tj = token_of(warp, i - L);
+                        for (int f = 0; f < F; ++f) {
+                            const int sj = slot_of(tj, f);
+                            if (sj >= 0 && sj < C)
+                                ptx::st_relaxed_sys(reinterpret_cast<uint32_t*>(c.peer[f] + g.f_slot_flag) + (size_t)ai * C + sj, ep);
+                        }
+                    }
                     ptx::st_release_cta_shared(&done_cnt[warp], i - L + 1);
                 }
             }
@@ -192,6 +238,17 @@ dispatch_kernel(const RankCtx c, const AttnWs ws, const DispatchArgs a, const Di
         }
         if (lane == 0) {
             ptx::bulk_wait<0>();
+            if (a.flag_mode == 1 && ok) {
+                ptx::fence_proxy_async_global();
+                for (int j = (n_w > L ? n_w - L : 0); j < n_w; ++j) {
+                    const int tj = token_of(warp, j);
+                    for (int f = 0; f < F; ++f) {
+                        const int sj = slot_of(tj, f);
+                        if (sj >= 0 && sj < C)
+                            ptx::st_relaxed_sys(reinterpret_cast<uint32_t*>(c.peer[f] + g.f_slot_flag) + (size_t)ai * C + sj, ep);
+                    }
+                }
+            }
             ptx::st_release_cta_shared(&done_cnt[warp], ok ? n_w : -1);
         }
     } else {
@@ -224,10 +281,11 @@ dispatch_kernel(const RankCtx c, const AttnWs ws, const DispatchArgs a, const Di
                 aborted = true;
                 d = flagged;
             }
+            if (d > flagged && a.flag_mode == 1) flagged = d;      // the data warps already did it
             if (d > flagged) {
                 ptx::fence_acq_rel_sys();
                 for (int j = flagged; j < d; ++j) {
-                    const int t = t0 + lane + j * ND;
+                    const int t = token_of(lane, j);
                     for (int f = 0; f < F; ++f) {
                         const int s = slot_of(t, f);
                         if (s >= 0 && s < C)

@@ -1,20 +1,24 @@
 // Grouped expert GEMM on tcgen05: C[rows, N] = A[rows, K] * W_e[N, K]^T for the expert-major
 // rows that worker_receive returns, one weight matrix per local expert.
 //
-// Layout of a CTA (192 threads, persistent over output tiles):
-//   warp 0      TMA producer: tensor-map loads of a 128 x BK tile of A and a 128 x BK tile of
+// Layout of a CTA (576 threads, persistent over 128 x 256 output tiles):
+//   warp 0      TMA producer: tensor-map loads of a 128 x BK tile of A and a 256 x BK tile of
 //               the expert's W into a ring of 128-byte-swizzled shared-memory stages
-//   warp 1      allocates tensor memory, then one elected lane issues tcgen05.mma for every
-//               stage and commits stage-free / accumulator-ready mbarriers
-//   warps 2..5  epilogue: tcgen05.ld the fp32 accumulator (thread = tile row), apply the
-//               block scales (FP8), SwiGLU and the routing weight, store BF16
-// Two accumulators in TMEM let the MMAs of the next tile (BF16) or the next K block (FP8) run
-// while the epilogue warps drain the previous one.
+//   warp 1      allocates tensor memory, then one elected lane issues tcgen05.mma (M 128, N 256)
+//               for every stage and commits stage-free / accumulator-ready mbarriers
+//   warps 2..17 epilogue: tcgen05.ld the fp32 accumulator (thread = tile row, one 64-column
+//               part per warp), apply the block scales (FP8), SwiGLU and the routing weight,
+//               store BF16.  Sixteen warps keep the per-K-block promotion of the FP8 path
+//               (256 x 128 FMAs) shorter than the MMAs it overlaps with.
+// Two 256-column accumulators fill tensor memory and let the MMAs of the next tile (BF16) or
+// the next K block (FP8) run while the epilogue warps drain the previous one.
 //
 // BF16 mode: kind::f16, BK = 64, one commit per tile.
 // FP8 mode:  kind::f8f6f4 on e4m3 with fp32 scales: one scale per row and 128 columns of A,
 //            one per 128 x 128 block of W.  Every 128-deep K block is multiplied into a fresh
 //            TMEM accumulator and promoted by the epilogue warps: acc += tmem * a_s * w_s.
+// SwiGLU:    gate and up rows of W alternate in blocks of 32, so every 64-column part of a tile
+//            holds 32 gate columns followed by their 32 up columns; the output has N/2 columns.
 //
 // Expert segments start on multiples of `alignment` rows (a multiple of 128), so a 128-row
 // tile never straddles two experts; tiles past an expert's last row are skipped, rows past it
@@ -30,11 +34,13 @@ namespace afdep {
 
 namespace {
 
-constexpr int BM = 128, BN = 128;
-constexpr int kThreads = 192;
-constexpr int kStageBytes = 2 * BM * 128;     // A tile + W tile, 128-byte rows
-constexpr int kStages = 6;
-constexpr int kTmemCols = 256;                // two 128-column fp32 accumulators
+constexpr int BM = 128, BN = 256;
+constexpr int HN = 64;                        // columns one epilogue warp handles
+constexpr int kEpiWarps = 4 * (BN / HN);      // four lane quarters times the column parts
+constexpr int kThreads = (2 + kEpiWarps) * 32;
+constexpr int kStageBytes = (BM + BN) * 128;  // A tile + W tile, 128-byte rows
+constexpr int kStages = 4;
+constexpr int kTmemCols = 512;                // two 256-column fp32 accumulators
 constexpr unsigned kSpinLimit = 1u << 28;     // try_wait probes before a wait gives up
 
 struct Ctrl {
@@ -71,7 +77,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     constexpr int BK = kFp8 ? 128 : 64;          // elements per 128-byte row
     const int num_kb = p.K / BK;
-    const int n_tiles = p.N / BN;
+    const int n_tiles = (p.N + BN - 1) / BN;     // the last tile may be half empty (N a multiple of 128)
 
     // ---- set-up: barriers, tile schedule, tensor memory --------------------------------
     if (tid == 0) {
@@ -81,7 +87,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
         for (int b = 0; b < 2; ++b) {
             ptx::mbar_init(&ctrl->acc_full[b], 1);
-            ptx::mbar_init(&ctrl->acc_empty[b], 4);     // one arrival per epilogue warp
+            ptx::mbar_init(&ctrl->acc_empty[b], kEpiWarps);     // one arrival per epilogue warp
         }
         ctrl->failed = 0;
         ptx::fence_mbar_init();
@@ -198,35 +204,41 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else {
         // ------------------------------------------------------------------ epilogue warps
         const int quarter = warp & 3;            // TMEM lanes this warp may touch: [32 * quarter, +32)
+        const int half = (warp - 2) >> 2;        // which 64 columns of the tile this warp handles
         const int r_in_tile = quarter * 32 + lane;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
         int acc_use = 0;
         for (int w = blockIdx.x; w < total_work && !*failed; w += gridDim.x) {
             int e, row0, col0;
             decode(w, e, row0, col0);
+            const int hcol0 = col0 + half * HN;                 // first column of this warp's half
+            const bool half_ok = hcol0 < p.N;
             const int row = row0 + r_in_tile;
-            const bool row_ok = row < p.ends[e] && row < p.rows;
-            float acc[kFp8 ? BN : 1];
+            const bool row_ok = row < p.ends[e] && row < p.rows && half_ok;
+            float acc[kFp8 ? HN : 1];
             if (kFp8) {
 #pragma unroll
-                for (int c = 0; c < BN; ++c) acc[kFp8 ? c : 0] = 0.f;
+                for (int c = 0; c < HN; ++c) acc[kFp8 ? c : 0] = 0.f;
             }
             bool ok = true;
             if (kFp8) {
                 // promotion: one fresh accumulator per 128-deep K block
                 const float* a_sc = p.a_scale + (size_t)(row_ok ? row : 0) * p.a_scale_s0;
-                const float* w_sc = p.w_scale + ((size_t)e * (p.N / 128) + col0 / 128) * (p.K / 128);
+                const float* w_sc = p.w_scale + ((size_t)e * (p.N / 128) + (half_ok ? hcol0 / 128 : 0)) * (p.K / 128);
+                float s_next = a_sc[0] * w_sc[0];
                 for (int kb = 0; kb < num_kb; ++kb) {
                     const int buf = acc_use & 1;
-                    const float s = a_sc[(size_t)kb * p.a_scale_s1] * w_sc[kb];
+                    const float s = s_next;
+                    if (kb + 1 < num_kb) s_next = a_sc[(size_t)(kb + 1) * p.a_scale_s1] * w_sc[kb + 1];
                     if (!wait_bar(&ctrl->acc_full[buf], (acc_use >> 1) & 1u, failed)) {
                         ok = false;
                         break;
                     }
                     tc::fence_after_sync();
 #pragma unroll
-                    for (int ch = 0; ch < BN / 32; ++ch) {
+                    for (int ch = 0; ch < HN / 32; ++ch) {
                         uint32_t v[32];
-                        tc::tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + ch * 32), v);
+                        tc::tmem_ld32(tmem + lane_base + (uint32_t)(buf * BN + half * HN + ch * 32), v);
                         tc::tmem_ld_wait();
 #pragma unroll
                         for (int c = 0; c < 32; ++c) acc[kFp8 ? ch * 32 + c : 0] += __uint_as_float(v[c]) * s;
@@ -244,24 +256,24 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 if (!wait_bar(&ctrl->acc_full[buf], (acc_use >> 1) & 1u, failed)) break;
                 tc::fence_after_sync();
             }
-            // ---- write the tile: thread = one row, 32 columns at a time -------------------
+            // ---- write the half tile: thread = one row, 32 columns at a time -----------------
             const float rs = (p.row_scale != nullptr && row_ok) ? p.row_scale[row] : 1.f;
             __nv_bfloat16* out_row = p.out + (size_t)(row_ok ? row : 0) * p.ldc;
+            const uint32_t tbase = tmem + lane_base + (uint32_t)(buf * BN + half * HN);
             if (p.swiglu) {
-                // columns [0, 64) of the tile are gate, [64, 128) the matching up projections
-#pragma unroll
-                for (int ch = 0; ch < 2; ++ch) {
+                // columns [0, 32) of the part are gate, [32, 64) the matching up projections
+                {
                     float gt[32], up[32];
                     if (kFp8) {
 #pragma unroll
                         for (int c = 0; c < 32; ++c) {
-                            gt[c] = acc[kFp8 ? ch * 32 + c : 0];
-                            up[c] = acc[kFp8 ? 64 + ch * 32 + c : 0];
+                            gt[c] = acc[kFp8 ? c : 0];
+                            up[c] = acc[kFp8 ? 32 + c : 0];
                         }
                     } else {
                         uint32_t v0[32], v1[32];
-                        tc::tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + ch * 32), v0);
-                        tc::tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + 64 + ch * 32), v1);
+                        tc::tmem_ld32(tbase, v0);
+                        tc::tmem_ld32(tbase + 32u, v1);
                         tc::tmem_ld_wait();
 #pragma unroll
                         for (int c = 0; c < 32; ++c) {
@@ -270,7 +282,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         }
                     }
                     if (row_ok) {
-                        __nv_bfloat16* dst = out_row + col0 / 2 + ch * 32;
+                        __nv_bfloat16* dst = out_row + hcol0 / 2;
 #pragma unroll
                         for (int c = 0; c < 32; c += 8) {
                             uint4 pk;
@@ -285,20 +297,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 }
             } else {
 #pragma unroll
-                for (int ch = 0; ch < BN / 32; ++ch) {
+                for (int ch = 0; ch < HN / 32; ++ch) {
                     float val[32];
                     if (kFp8) {
 #pragma unroll
                         for (int c = 0; c < 32; ++c) val[c] = acc[kFp8 ? ch * 32 + c : 0];
                     } else {
                         uint32_t v[32];
-                        tc::tmem_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + ch * 32), v);
+                        tc::tmem_ld32(tbase + (uint32_t)(ch * 32), v);
                         tc::tmem_ld_wait();
 #pragma unroll
                         for (int c = 0; c < 32; ++c) val[c] = __uint_as_float(v[c]);
                     }
                     if (row_ok) {
-                        __nv_bfloat16* dst = out_row + col0 + ch * 32;
+                        __nv_bfloat16* dst = out_row + hcol0 + ch * 32;
 #pragma unroll
                         for (int c = 0; c < 32; c += 8) {
                             uint4 pk;

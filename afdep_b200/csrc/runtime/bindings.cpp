@@ -15,6 +15,7 @@
 #include <torch/extension.h>
 
 #include <chrono>
+#include <cstdlib>
 #include <memory>
 #include <thread>
 
@@ -117,8 +118,9 @@ public:
             aws_.ticket = reinterpret_cast<unsigned*>(fl + 24);
             const int64_t ncols = ffn + num_experts;
             agg_ = torch::zeros({(int64_t)max_dispatch_ctas() * ncols}, torch::TensorOptions().dtype(torch::kInt64).device(torch::kCUDA, device_));
-            scratch_ = torch::zeros({(int64_t)capacity * (2 * top_k + ffn)}, i32);
+            scratch_ = torch::zeros({(int64_t)capacity * (2 * top_k + ffn) + max_dispatch_ctas()}, i32);
             int* s = scratch_.data_ptr<int>();
+            aws_.chunk_done = reinterpret_cast<unsigned*>(s + (size_t)capacity * (2 * top_k + ffn));
             aws_.agg = reinterpret_cast<unsigned long long*>(agg_.data_ptr<int64_t>());
             aws_.route_e = s;
             aws_.route_pos = s + (size_t)capacity * top_k;
@@ -176,6 +178,8 @@ public:
         a.ids = reinterpret_cast<const long long*>(ids.data_ptr<int64_t>());
         a.weights = weights.data_ptr<float>();
         a.T = T;
+        static const int flag_mode = std::getenv("AFDEP_FLAG_MODE") ? std::atoi(std::getenv("AFDEP_FLAG_MODE")) : 0;
+        a.flag_mode = flag_mode;
         if (geo_.fp8) {
             TORCH_CHECK(x_scale.has_value(), "FP8 dispatch needs scales");
             a.x_scale = x_scale->data_ptr<float>();
@@ -469,13 +473,13 @@ py::tuple route_layout(const torch::Tensor& ids, int64_t num_experts, int64_t ff
 
 namespace {
 
-// Tensor map of a row-major [rows, cols] matrix with 128-byte-swizzled boxes of 128 rows by
-// 128 bytes, the tile shape the grouped GEMM's shared-memory descriptors expect.
-CUtensorMap make_tile_map(const void* base, int64_t rows, int64_t cols, int elem_bytes) {
+// Tensor map of a row-major [rows, cols] matrix with 128-byte-swizzled boxes of `box_rows`
+// rows by 128 bytes, the tile shape the grouped GEMM's shared-memory descriptors expect.
+CUtensorMap make_tile_map(const void* base, int64_t rows, int64_t cols, int elem_bytes, int box_rows) {
     CUtensorMap map;
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)cols * (cuuint64_t)elem_bytes};
-    const cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), 128u};
+    const cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1u, 1u};
     const CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     drv_check(AFDEP_DRV(cuTensorMapEncodeTiled)(&map, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
@@ -535,8 +539,8 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& w, const
     }
     if (rows == 0) return out;
     const int elem = fp8 ? 1 : 2;
-    const CUtensorMap map_a = make_tile_map(a.data_ptr(), rows, K, elem);
-    const CUtensorMap map_w = make_tile_map(w.data_ptr(), E * N, K, elem);
+    const CUtensorMap map_a = make_tile_map(a.data_ptr(), rows, K, elem, 128);
+    const CUtensorMap map_w = make_tile_map(w.data_ptr(), E * N, K, elem, 256);
     int sms = 0;
     rt_check(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, a.get_device()), "device attribute");
     const int grid = ctas > 0 ? (int)ctas : sms;

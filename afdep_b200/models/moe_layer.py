@@ -33,7 +33,7 @@ from ..ops import grouped_gemm as gg
 class ExpertWeights:
     """Weights of the local experts of one FFN rank, in the layouts the kernels consume."""
 
-    w_gate_up: torch.Tensor            # [E, 2I, H] bf16 or e4m3, gate/up interleaved in 64-row blocks
+    w_gate_up: torch.Tensor            # [E, 2I, H] bf16 or e4m3, gate/up interleaved in 32-row blocks
     w_gate_up_scale: torch.Tensor | None   # [E, 2I/128, H/128] fp32 (FP8 only)
     w_down: torch.Tensor               # [E, H, I] bf16
     intermediate: int

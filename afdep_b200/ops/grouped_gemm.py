@@ -7,7 +7,7 @@
 
 Operands are BF16, or e4m3 with fp32 block scales (``a_scale [rows, K/128]`` per row and 128
 columns, ``w_scale [experts, N/128, K/128]`` per 128 x 128 block).  ``swiglu=True`` expects the
-gate and up projections interleaved in blocks of 64 rows of ``w`` (see ``interleave_gate_up``)
+gate and up projections interleaved in blocks of 32 rows of ``w`` (see ``interleave_gate_up``)
 and returns ``silu(gate) * up`` with ``N/2`` columns; ``row_scale`` multiplies every output
 row (the routing weight).  Rows outside the expert segments are left untouched.
 """
@@ -15,6 +15,8 @@ row (the routing weight).  Rows outside the expert segments are left untouched.
 from __future__ import annotations
 
 import torch
+
+GATE_UP_BLOCK = 32   # rows of gate, then rows of up, alternating in the fused gate|up matrix
 
 
 def grouped_gemm(a, w, ends, alignment: int, *, swiglu: bool = False, row_scale=None, a_scale=None, w_scale=None, out=None, ctas: int = 0):
@@ -24,20 +26,11 @@ def grouped_gemm(a, w, ends, alignment: int, *, swiglu: bool = False, row_scale=
 
 
 def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
-    """[E, I, K] gate and up -> [E, 2I, K] with alternating 64-row blocks gate, up, gate, up, ..."""
+    """[E, I, K] gate and up -> [E, 2I, K] with alternating 32-row blocks gate, up, gate, up, ..."""
     E, I, K = w_gate.shape
-    g = w_gate.reshape(E, I // 64, 64, K)
-    u = w_up.reshape(E, I // 64, 64, K)
+    g = w_gate.reshape(E, I // GATE_UP_BLOCK, GATE_UP_BLOCK, K)
+    u = w_up.reshape(E, I // GATE_UP_BLOCK, GATE_UP_BLOCK, K)
     return torch.stack((g, u), dim=2).reshape(E, 2 * I, K).contiguous()
-
-
-def interleave_gate_up_scales(s_gate: torch.Tensor, s_up: torch.Tensor) -> torch.Tensor:
-    """Block scales of the interleaved matrix.  A 128-row block of it holds 64 gate and 64 up
-    rows from the same 128-row block pair, so gate and up must share their 128 x 128 scale:
-    pass matrices quantized with ``quantize_weight_blocks(..., pair=...)`` or use this on
-    per-64-row scales [E, I/64, K/128]."""
-    E, B, Kb = s_gate.shape
-    return torch.maximum(s_gate, s_up).reshape(E, B, Kb).contiguous()
 
 
 def segment_starts(ends: torch.Tensor, alignment: int) -> torch.Tensor:
@@ -63,7 +56,7 @@ def reference_grouped_gemm(a, w, ends, alignment, *, swiglu=False, row_scale=Non
             continue
         y = af[s:t] @ wf[e].T
         if swiglu:
-            y = y.view(t - s, N // 128, 2, 64)
+            y = y.view(t - s, N // (2 * GATE_UP_BLOCK), 2, GATE_UP_BLOCK)
             y = (torch.nn.functional.silu(y[:, :, 0]) * y[:, :, 1]).reshape(t - s, N // 2)
         if row_scale is not None:
             y = y * row_scale[s:t].float()[:, None]

@@ -54,6 +54,7 @@ def parse_args():
     p.add_argument("--num-sms", type=int, default=0)
     p.add_argument("--graph", action="store_true", help="replay each step from a CUDA graph")
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--trace", action="store_true", help="print per-kernel device time stamps of the last step (native transport)")
     return p.parse_args()
 
 
@@ -66,57 +67,69 @@ def topology(n: int, config: str) -> tuple[int, int]:
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons while the timed region runs (read-only)."""
+    """SM clock and throttle reasons while the timed region runs.  Read-only NVML queries from
+    a background thread (every 2 ms); falls back to one `nvidia-smi` query if NVML is missing."""
 
-    QUERY = (
-        "index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-        "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
-    )
+    REASONS = {
+        "hw_slowdown": 0x8,
+        "sw_power_cap": 0x4,
+        "sw_thermal_slowdown": 0x20,
+        "hw_thermal_slowdown": 0x40,
+    }
 
     def __init__(self, device_index: int) -> None:
-        self.proc, self.index = None, device_index
+        self.index, self.samples, self.reasons, self.max_mhz = device_index, [], set(), None
+        self._stop, self._thread, self._nvml = False, None, None
+
+    def _loop(self) -> None:
+        nv, h = self._nvml, self._handle
+        while not self._stop:
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                for name, bit in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:  # noqa: BLE001 - sampling must never break the benchmark
+                pass
+            time.sleep(0.002)
 
     def start(self) -> None:
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50", "-i", str(self.index)],
-                stdout=subprocess.PIPE,
-                stderr=subprocess.DEVNULL,
-                text=True,
-            )
-            self.first = self.proc.stdout.readline()   # blocks until the sampler is really running
-        except OSError:
-            self.proc = None
+            import pynvml as nv
+
+            nv.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            index = int(visible.split(",")[self.index]) if visible and visible.split(",")[self.index].isdigit() else self.index
+            self._handle = nv.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(self._handle, nv.NVML_CLOCK_SM)
+            self._nvml = nv
+            import threading
+
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        except Exception:  # noqa: BLE001
+            self._nvml = None
 
     def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
+        if self._nvml is not None:
+            self._stop = True
+            self._thread.join(timeout=1.0)
+            return {
+                "sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz,
+                "samples": len(self.samples),
+                "reasons": sorted(self.reasons),
+                "source": "nvml",
+            }
         try:
-            out, _ = self.proc.communicate(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-            out, _ = self.proc.communicate()
-        sm, mx, reasons = [], [], set()
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for line in [getattr(self, "first", "")] + out.splitlines():
-            f = [s.strip() for s in line.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1]))
-                mx.append(float(f[2]))
-            except ValueError:
-                continue
-            for name, v in zip(names, f[5:9]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        return {
-            "sm_mhz": statistics.median(sm) if sm else None,
-            "sm_max_mhz": max(mx) if mx else None,
-            "samples": len(sm),
-            "reasons": sorted(reasons),
-        }
+            out = subprocess.run(
+                ["nvidia-smi", "--query-gpu=clocks.sm,clocks.max.sm", "--format=csv,noheader,nounits", "-i", str(self.index)],
+                capture_output=True, text=True, timeout=10,
+            ).stdout.strip().split(",")
+            return {"sm_mhz": float(out[0]), "sm_max_mhz": float(out[1]), "samples": 1, "reasons": [], "source": "nvidia-smi after the run"}
+        except Exception:  # noqa: BLE001
+            return {"sm_mhz": None, "sm_max_mhz": None, "samples": 0, "reasons": ["clock query unavailable"]}
 
 
 def reference_arm(args) -> None:
@@ -323,6 +336,9 @@ def main() -> None:
         torch.cuda.synchronize()
         return [a.elapsed_time(b) for a, b in pairs[warmup:]]
 
+    traces = []
+    if args.trace and args.impl == "ours":
+        traces = [(s["buf"].rank, s["buf"]._t._nb.trace(True)) for s in state]
     torch.cuda.synchronize()
     if multi:
         dist.barrier()
@@ -423,6 +439,29 @@ def main() -> None:
             "h2d_bytes_per_step": hi,
             "d2h_bytes_per_step": 4 * n,
         }
+    if traces:
+        names = ["dispatch", "receive", "reply", "collect"]
+        lines = []
+        for r, tr in traces:
+            tr = tr.cpu()
+            for k in range(4):
+                t = tr[k]
+                used = t[:, 0] > 0
+                if not used.any():
+                    continue
+                t = t[used]
+                s0 = int(t[:, 0].min())
+                p1 = (int(t[:, 1].max()) - s0) / 1e3 if (t[:, 1] > 0).any() else float("nan")
+                lines.append(
+                    f"rank {r} {names[k]:9s} ctas={int(used.sum()):3d} start_ns={s0 % 10**9:9d} phase1_end={p1:7.1f}us "
+                    f"first_cta_end={(int(t[:, 2].min()) - s0) / 1e3:7.1f}us last_cta_end={(int(t[:, 2].max()) - s0) / 1e3:7.1f}us"
+                )
+        if multi:
+            alll = [None] * n
+            dist.all_gather_object(alll, lines)
+            lines = [l for part in alll for l in part]
+        if rank == 0:
+            print("\n".join(lines), file=sys.stderr)
     for s in state:
         s["buf"].check()
     if multi:

@@ -235,3 +235,16 @@ def test_cuda_graph_replay_with_changed_inputs():
             b.check()
     finally:
         world.close()
+
+
+def test_dedicated_comm_stream_option():
+    """Exchange kernels on a separate high-priority stream, ordered with events."""
+    cfg = Config(32, 512, 8, 2, 2, 2, expert_alignment=8)
+    world = make_world(cfg, use_comm_stream=True)
+    try:
+        assert world.buffers[0].comm_stream != torch.cuda.current_stream()
+        for epoch in range(2):
+            batches = [synthetic.exact_batch(cfg, 32, a, epoch) for a in range(2)]
+            run_and_check(world, cfg, batches)
+    finally:
+        world.close()

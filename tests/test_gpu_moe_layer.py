@@ -60,7 +60,7 @@ def test_moe_layer_matches_dense_reference(payload, mode):
                     if not tok.any():
                         continue
                     y = xf[tok] @ gu[le].T
-                    y = y.view(y.shape[0], -1, 2, 64)
+                    y = y.view(y.shape[0], -1, 2, 32)
                     h = (torch.nn.functional.silu(y[:, :, 0]) * y[:, :, 1]).reshape(y.shape[0], -1)
                     o = h.to(torch.bfloat16).float() @ wt.w_down[le].float().T
                     want[tok] += o * (w * sel)[tok].sum(dim=1, keepdim=True)

@@ -148,3 +148,23 @@ def _withheld_reply(rank, world):
 @pytest.mark.multigpu(2)
 def test_withheld_reply_times_out_cleanly():
     run_ranks(_withheld_reply, 2, timeout=300)
+
+
+def _nccl_baseline(rank, world, ffn, payload):
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    attn = world - ffn
+    cfg = Config(128, 512, 16, 4, ffn, attn, expert_alignment=16, payload=payload)
+    buf = Buffer(group=dist.group.WORLD, config=cfg, backend="nccl")
+    for epoch in range(2):
+        batches = [synthetic.exact_batch(cfg, 128 - 9 * a, a, epoch) for a in range(attn)]
+        _exchange_once(buf, cfg, batches, tokens=128, read_host_counts=(epoch == 1))
+    buf.close()
+
+
+@pytest.mark.multigpu(2)
+@pytest.mark.parametrize("payload", ["bf16", "fp8"])
+def test_nccl_baseline_transport_matches_oracle(payload):
+    """The baseline the kernels are compared with must itself be a correct exchange."""
+    run_ranks(_nccl_baseline, 2, 1, payload, timeout=600)
