@@ -22,6 +22,7 @@
 #include "afdep/aux_api.h"
 #include "afdep/gemm_api.h"
 #include "afdep/kernels.h"
+#include "afdep/quant_api.h"
 #include "afdep/route_layout_api.h"
 #include "driver.hpp"
 #include "heap.hpp"
@@ -548,6 +549,28 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& w, const
     return out;
 }
 
+// (e4m3 [rows, K], fp32 scales [rows, K/128]) from bf16 rows; `limit` (optional int32 device
+// tensor, e.g. recv_count_psum[-1:]) marks the first row that need not be quantised.
+py::tuple quantize_rows_fp8(const torch::Tensor& x, const c10::optional<torch::Tensor>& limit) {
+    TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == torch::kBFloat16 && x.is_contiguous(), "x: contiguous CUDA bf16 [rows, K]");
+    const int64_t rows = x.size(0), K = x.size(1);
+    TORCH_CHECK(K % 128 == 0, "K must be a multiple of 128");
+    c10::cuda::CUDAGuard guard(x.device());
+    auto q = torch::empty({rows, K}, torch::TensorOptions().dtype(torch::kFloat8_e4m3fn).device(x.device()));
+    auto scale = torch::empty({rows, K / 128}, torch::TensorOptions().dtype(torch::kFloat32).device(x.device()));
+    const int* lim = nullptr;
+    if (limit.has_value()) {
+        TORCH_CHECK(limit->is_cuda() && limit->scalar_type() == torch::kInt32 && limit->numel() >= 1, "limit: int32 CUDA tensor");
+        lim = limit->data_ptr<int>();
+    }
+    int sms = 0;
+    rt_check(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, x.get_device()), "device attribute");
+    rt_check(launch_quantize_rows(x.data_ptr(), q.data_ptr(), scale.data_ptr<float>(), (int)rows, (int)K, scale.stride(0), scale.stride(1), lim,
+                                  sms * 8, at::cuda::getCurrentCUDAStream().stream()),
+             "quantize launch");
+    return py::make_tuple(q, scale);
+}
+
 }  // namespace afdep
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -558,6 +581,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("grouped_gemm", &afdep::grouped_gemm, py::arg("a"), py::arg("w"), py::arg("ends"), py::arg("alignment"),
           py::arg("swiglu") = false, py::arg("row_scale") = py::none(), py::arg("a_scale") = py::none(),
           py::arg("w_scale") = py::none(), py::arg("out") = py::none(), py::arg("ctas") = 0);
+    m.def("quantize_rows_fp8", &afdep::quantize_rows_fp8, py::arg("x"), py::arg("limit") = py::none());
     m.def("route_layout", &afdep::route_layout, py::arg("ids"), py::arg("num_experts"), py::arg("ffn_ranks"));
     py::class_<NativeBuffer>(m, "NativeBuffer")
         .def(py::init<int, int, int, int, int, int, int, bool, int, int, int, int, double, int64_t, const std::string&, bool>(),

@@ -70,8 +70,8 @@ def run_experts(received: ReceiveResult, weights: ExpertWeights, alignment: int,
     x, ends = received.recv_x, received.recv_count_psum
     fp8 = weights.mode == "fp8"
     if fp8 and x.dtype != torch.float8_e4m3fn:
-        # BF16 dispatch into FP8 experts: quantise on the FFN rank (one fused torch pass)
-        x, a_scale = gg.quantize_rows_fp8(x)
+        # BF16 dispatch into FP8 experts: quantise the live rows on the FFN rank (one kernel)
+        x, a_scale = gg.quantize_rows_fp8_cuda(x, ends[-1:])
     else:
         a_scale = received.recv_scale
     h = gg.grouped_gemm(x, weights.w_gate_up, ends, alignment, swiglu=True, a_scale=a_scale if fp8 else None,

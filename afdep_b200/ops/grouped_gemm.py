@@ -64,6 +64,14 @@ def reference_grouped_gemm(a, w, ends, alignment, *, swiglu=False, row_scale=Non
     return out
 
 
+def quantize_rows_fp8_cuda(x: torch.Tensor, limit: torch.Tensor | None = None):
+    """The same quantisation as ``quantize_rows_fp8`` in one CUDA kernel (bf16 input on the GPU).
+    ``limit``: optional int32 device tensor; rows at or beyond ``limit[0]`` are left unwritten."""
+    from .._native import load_native
+
+    return load_native().quantize_rows_fp8(x, limit)
+
+
 def quantize_rows_fp8(x: torch.Tensor):
     """e4m3 rows with one fp32 scale per row and 128 columns (amax / 448)."""
     rows, K = x.shape

@@ -85,6 +85,7 @@ class NativeTransport:
         # stream saves two cross-stream hops per call, which matters at decode latencies.
         want_stream = options.get("use_comm_stream", os.environ.get("AFDEP_COMM_STREAM", "0") not in ("0", ""))
         self._comm_stream = torch.cuda.Stream(device=self.device, priority=-1) if want_stream else None
+        self._nvtx = os.environ.get("AFDEP_NVTX", "0") not in ("0", "")
         if not self._loopback:
             self._connect_peers()
             torch.cuda.synchronize(self.device)
@@ -128,6 +129,16 @@ class NativeTransport:
     @property
     def comm_stream(self):
         return self._comm_stream if self._comm_stream is not None else self._torch.cuda.current_stream(self.device)
+
+    def _ranged(self, name: str, fn):
+        """NVTX range around a role call when AFDEP_NVTX=1 (for timelines; off by default)."""
+        if not self._nvtx:
+            return fn()
+        self._torch.cuda.nvtx.range_push(f"afdep.{name}")
+        try:
+            return fn()
+        finally:
+            self._torch.cuda.nvtx.range_pop()
 
     def _on_comm_stream(self, fn, *tensors):
         """Run ``fn`` on the communication stream, after everything queued on the current stream,
@@ -215,19 +226,22 @@ class NativeTransport:
         return self._empties()["out"]
 
     def source_dispatch(self, x, x_scale, ids, weights, *, bucket: int) -> None:
-        self._on_comm_stream(lambda: self._nb.source_dispatch(x, x_scale, ids, weights), x, x_scale, ids, weights)
+        self._ranged("source_dispatch", lambda: self._on_comm_stream(lambda: self._nb.source_dispatch(x, x_scale, ids, weights), x, x_scale, ids, weights))
 
     def source_collect(self, num_tokens: int):
-        return self._on_comm_stream(lambda: self._nb.source_collect(num_tokens))
+        return self._ranged("source_collect", lambda: self._on_comm_stream(lambda: self._nb.source_collect(num_tokens)))
 
     def worker_receive(self, *, bucket: int, read_host_counts: bool):
         rows = self.config.receive_rows(bucket)
-        return self._on_comm_stream(
-            lambda: self._nb.worker_receive(rows, read_host_counts, float(self.config.cpu_timeout_s), self._col_major_scale)
+        return self._ranged(
+            "worker_receive",
+            lambda: self._on_comm_stream(
+                lambda: self._nb.worker_receive(rows, read_host_counts, float(self.config.cpu_timeout_s), self._col_major_scale)
+            ),
         )
 
     def worker_reply(self, rows) -> None:
-        self._on_comm_stream(lambda: self._nb.worker_reply(rows), rows)
+        self._ranged("worker_reply", lambda: self._on_comm_stream(lambda: self._nb.worker_reply(rows), rows))
 
     def close(self) -> None:
         torch = self._torch

@@ -79,3 +79,19 @@ def test_fp8_block_scaled_grouped_gemm(swiglu):
     starts = gg.segment_starts(ends, 128).tolist()
     for s, t in zip(starts, ends.tolist()):
         torch.testing.assert_close(out[s:t].float(), ref[s:t], rtol=2e-2, atol=2e-2)
+
+
+def test_fp8_row_quantiser_matches_torch():
+    torch.manual_seed(3)
+    x = (torch.randn(300, 1024, device="cuda") * 3).bfloat16()
+    x[7] = 0                                         # an all-zero group must not divide by zero
+    limit = torch.tensor([257], dtype=torch.int32, device="cuda")
+    q, s = gg.quantize_rows_fp8_cuda(x, limit)
+    qr, sr = gg.quantize_rows_fp8(x)
+    torch.cuda.synchronize()
+    torch.testing.assert_close(s[:257], sr[:257], rtol=1e-6, atol=0)
+    # dequantised values agree to within one e4m3 step of the group's scale
+    dq = q[:257].float().view(257, -1, 128) * s[:257, :, None]
+    dr = qr[:257].float().view(257, -1, 128) * sr[:257, :, None]
+    assert (dq - dr).abs().max() <= (sr[:257].max() * 32)
+    assert torch.equal(q[:257].view(torch.uint8), qr[:257].view(torch.uint8)) or ((dq - dr).abs() > 0).float().mean() < 0.01
