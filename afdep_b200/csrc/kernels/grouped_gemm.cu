@@ -240,8 +240,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         uint32_t v[32];
                         tc::tmem_ld32(tmem + lane_base + (uint32_t)(buf * BN + half * HN + ch * 32), v);
                         tc::tmem_ld_wait();
+                        // packed fp32 FMAs (two per instruction on sm_100) halve the promotion's issue slots
+                        const float2 s2 = make_float2(s, s);
 #pragma unroll
-                        for (int c = 0; c < 32; ++c) acc[kFp8 ? ch * 32 + c : 0] += __uint_as_float(v[c]) * s;
+                        for (int c = 0; c < 32; c += 2) {
+                            const int i0 = kFp8 ? ch * 32 + c : 0;
+                            const float2 r = __ffma2_rn(make_float2(__uint_as_float(v[c]), __uint_as_float(v[c + 1])), s2,
+                                                        make_float2(acc[i0], acc[kFp8 ? i0 + 1 : 0]));
+                            acc[i0] = r.x;
+                            acc[kFp8 ? i0 + 1 : 0] = r.y;
+                        }
                     }
                     tc::fence_before_sync();
                     __syncwarp();

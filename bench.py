@@ -235,19 +235,35 @@ def main() -> None:
 
     # wire bytes per step (both directions) from the routes: one record per (token, FFN rank)
     el = cfg.experts_per_rank
-    records = 0
+    per_ffn = [0] * ffn          # records this process's attention ranks send to each FFN rank
+    egress = []                  # records leaving each local attention rank
     for s in state:
         if "ids_cpu" in s:
             ids = s["ids_cpu"]
             dest = torch.where(ids >= 0, ids // el, torch.full_like(ids, -1))
-            for f in range(ffn):
-                records += int((dest == f).any(dim=1).sum())
+            mine = [int((dest == f).any(dim=1).sum()) for f in range(ffn)]
+            per_ffn = [p + m for p, m in zip(per_ffn, mine)]
+            egress.append(sum(mine))
     if multi:
-        allrec = [None] * n
-        dist.all_gather_object(allrec, records)
-        records = sum(allrec)
+        gathered = [None] * n
+        dist.all_gather_object(gathered, (per_ffn, egress))
+        per_ffn = [sum(g[0][f] for g in gathered) for f in range(ffn)]
+        egress = [e for g in gathered for e in g[1]]
+    records = sum(per_ffn)
     row_out = cfg.hidden_size * (1 if cfg.is_fp8 else 2) + (cfg.scale_groups * 4 if cfg.is_fp8 else 0)
-    wire_bytes = records * (row_out + cfg.hidden_size * 2)
+    row_back = cfg.hidden_size * 2
+    wire_bytes = records * (row_out + row_back)
+    # NVLink roofline: bytes through the busiest port (an attention rank's egress or an FFN
+    # rank's ingress on dispatch, the reverse on combine) over the measured 770 GB/s per direction.
+    busiest = max(max(egress, default=0), max(per_ffn, default=0))
+    roofline = {
+        "busiest_port_records": busiest,
+        "dispatch_us_at_770GBs": round(busiest * row_out / 770e9 * 1e6, 2),
+        "combine_us_at_770GBs": round(busiest * row_back / 770e9 * 1e6, 2),
+        "dispatch_us_at_900GBs_nominal": round(busiest * row_out / 900e9 * 1e6, 2),
+        "combine_us_at_900GBs_nominal": round(busiest * row_back / 900e9 * 1e6, 2),
+        "note": "colocated ranks share one GPU: no NVLink, HBM-bound" if not multi else "",
+    }
 
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     ordered = sorted(state, key=lambda s: 0 if s["buf"].role == "attention" else 1)
@@ -421,6 +437,10 @@ def main() -> None:
             else None
         ),
         "phases": phases,
+        "roofline": dict(
+            roofline,
+            fraction_of_nvlink_roofline=round((roofline["dispatch_us_at_770GBs"] + roofline["combine_us_at_770GBs"]) / (ms_per_step * 1e3), 3),
+        ),
         "clocks": clocks,
         "gpu_launches": launches,
         "wall_s_timed_region": round(t_wall1 - t_wall0, 3),
