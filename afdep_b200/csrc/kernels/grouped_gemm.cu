@@ -1,15 +1,16 @@
 // Grouped expert GEMM on tcgen05: C[rows, N] = A[rows, K] * W_e[N, K]^T for the expert-major
 // rows that worker_receive returns, one weight matrix per local expert.
 //
-// Layout of a CTA (576 threads, persistent over 128 x 256 output tiles):
+// Layout of a CTA (persistent over 128 x 256 output tiles):
 //   warp 0      TMA producer: tensor-map loads of a 128 x BK tile of A and a 256 x BK tile of
 //               the expert's W into a ring of 128-byte-swizzled shared-memory stages
 //   warp 1      allocates tensor memory, then one elected lane issues tcgen05.mma (M 128, N 256)
 //               for every stage and commits stage-free / accumulator-ready mbarriers
-//   warps 2..17 epilogue: tcgen05.ld the fp32 accumulator (thread = tile row, one 64-column
-//               part per warp), apply the block scales (FP8), SwiGLU and the routing weight,
-//               store BF16.  Sixteen warps keep the per-K-block promotion of the FP8 path
-//               (256 x 128 FMAs) shorter than the MMAs it overlaps with.
+//   epilogue    warps 2..: tcgen05.ld the fp32 accumulator (thread = tile row, one column part
+//               per warp), apply the block scales (FP8), SwiGLU and the routing weight, store
+//               BF16.  BF16 uses sixteen warps of 64 columns; FP8 keeps 128 running sums per
+//               thread for the promotion and uses eight warps of 128 columns (measured: sixteen
+//               warps cap the kernel at 96 registers and spill the sums).
 // Two 256-column accumulators fill tensor memory and let the MMAs of the next tile (BF16) or
 // the next K block (FP8) run while the epilogue warps drain the previous one.
 //
@@ -35,9 +36,10 @@ namespace afdep {
 namespace {
 
 constexpr int BM = 128, BN = 256;
-constexpr int HN = 64;                        // columns one epilogue warp handles
-constexpr int kEpiWarps = 4 * (BN / HN);      // four lane quarters times the column parts
-constexpr int kThreads = (2 + kEpiWarps) * 32;
+// columns one epilogue warp handles / epilogue warps / threads, per operand type
+__host__ __device__ constexpr int part_cols(bool fp8) { return fp8 ? 128 : 64; }
+__host__ __device__ constexpr int epi_warps(bool fp8) { return 4 * (BN / part_cols(fp8)); }      // four lane quarters times the column parts
+__host__ __device__ constexpr int cta_threads(bool fp8) { return (2 + epi_warps(fp8)) * 32; }
 constexpr int kStageBytes = (BM + BN) * 128;  // A tile + W tile, 128-byte rows
 constexpr int kStages = 4;
 constexpr int kTmemCols = 512;                // two 256-column fp32 accumulators
@@ -67,7 +69,7 @@ __device__ __forceinline__ bool wait_bar(uint64_t* bar, unsigned parity, volatil
 __device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
 
 template <bool kFp8>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(cta_threads(kFp8), 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const GroupedGemmArgs p) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -76,6 +78,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem + kStages * kStageBytes);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     constexpr int BK = kFp8 ? 128 : 64;          // elements per 128-byte row
+    constexpr int HN = part_cols(kFp8);
+    constexpr int kEpiWarps = epi_warps(kFp8);
     const int num_kb = p.K / BK;
     const int n_tiles = (p.N + BN - 1) / BN;     // the last tile may be half empty (N a multiple of 128)
 
@@ -204,7 +208,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     } else {
         // ------------------------------------------------------------------ epilogue warps
         const int quarter = warp & 3;            // TMEM lanes this warp may touch: [32 * quarter, +32)
-        const int half = (warp - 2) >> 2;        // which 64 columns of the tile this warp handles
+        const int half = (warp - 2) >> 2;        // which HN columns of the tile this warp handles
         const int r_in_tile = quarter * 32 + lane;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
         int acc_use = 0;
@@ -269,19 +273,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             __nv_bfloat16* out_row = p.out + (size_t)(row_ok ? row : 0) * p.ldc;
             const uint32_t tbase = tmem + lane_base + (uint32_t)(buf * BN + half * HN);
             if (p.swiglu) {
-                // columns [0, 32) of the part are gate, [32, 64) the matching up projections
-                {
+                // every 64 columns hold 32 gate columns followed by their 32 up columns
+#pragma unroll
+                for (int sub = 0; sub < HN / 64; ++sub) {
                     float gt[32], up[32];
                     if (kFp8) {
 #pragma unroll
                         for (int c = 0; c < 32; ++c) {
-                            gt[c] = acc[kFp8 ? c : 0];
-                            up[c] = acc[kFp8 ? 32 + c : 0];
+                            gt[c] = acc[kFp8 ? sub * 64 + c : 0];
+                            up[c] = acc[kFp8 ? sub * 64 + 32 + c : 0];
                         }
                     } else {
                         uint32_t v0[32], v1[32];
-                        tc::tmem_ld32(tbase, v0);
-                        tc::tmem_ld32(tbase + 32u, v1);
+                        tc::tmem_ld32(tbase + (uint32_t)(sub * 64), v0);
+                        tc::tmem_ld32(tbase + (uint32_t)(sub * 64 + 32), v1);
                         tc::tmem_ld_wait();
 #pragma unroll
                         for (int c = 0; c < 32; ++c) {
@@ -290,7 +295,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         }
                     }
                     if (row_ok) {
-                        __nv_bfloat16* dst = out_row + hcol0 / 2;
+                        __nv_bfloat16* dst = out_row + hcol0 / 2 + sub * 32;
 #pragma unroll
                         for (int c = 0; c < 32; c += 8) {
                             uint4 pk;
@@ -367,9 +372,9 @@ cudaError_t launch_grouped_gemm(const CUtensorMap& map_a, const CUtensorMap& map
         configured = true;
     }
     if (args.fp8)
-        grouped_gemm_kernel<true><<<ctas, kThreads, kSmemBytes, stream>>>(map_a, map_w, args);
+        grouped_gemm_kernel<true><<<ctas, cta_threads(true), kSmemBytes, stream>>>(map_a, map_w, args);
     else
-        grouped_gemm_kernel<false><<<ctas, kThreads, kSmemBytes, stream>>>(map_a, map_w, args);
+        grouped_gemm_kernel<false><<<ctas, cta_threads(false), kSmemBytes, stream>>>(map_a, map_w, args);
     return cudaGetLastError();
 }
 

@@ -87,11 +87,12 @@ def test_fp8_row_quantiser_matches_torch():
     x[7] = 0                                         # an all-zero group must not divide by zero
     limit = torch.tensor([257], dtype=torch.int32, device="cuda")
     q, s = gg.quantize_rows_fp8_cuda(x, limit)
-    qr, sr = gg.quantize_rows_fp8(x)
+    _, sr = gg.quantize_rows_fp8(x)
     torch.cuda.synchronize()
-    torch.testing.assert_close(s[:257], sr[:257], rtol=1e-6, atol=0)
-    # dequantised values agree to within one e4m3 step of the group's scale
+    torch.testing.assert_close(s[:257], sr[:257], rtol=1e-5, atol=0)
+    # every value comes back within half an e4m3 step (2^-4 relative, or the group's smallest step)
+    xf = x[:257].float().view(257, -1, 128)
     dq = q[:257].float().view(257, -1, 128) * s[:257, :, None]
-    dr = qr[:257].float().view(257, -1, 128) * sr[:257, :, None]
-    assert (dq - dr).abs().max() <= (sr[:257].max() * 32)
-    assert torch.equal(q[:257].view(torch.uint8), qr[:257].view(torch.uint8)) or ((dq - dr).abs() > 0).float().mean() < 0.01
+    bound = xf.abs() * 0.0625 + s[:257, :, None] * 2.0 ** -9 + 1e-30
+    assert ((dq - xf).abs() <= bound).all()
+    assert (dq[7] == 0).all()
