@@ -99,12 +99,13 @@ collect_kernel(const RankCtx c, const AttnWs ws, unsigned char* __restrict__ out
                 float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
                 for (int rr = 0; rr < nrows; ++rr) {
                     const uint4 x = *reinterpret_cast<const uint4*>(buf + (size_t)rr * g.row_bytes + (size_t)v * 16);
-                    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&x);
+                    const unsigned w[4] = {x.x, x.y, x.z, x.w};
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float2 fl = __bfloat1622float2(p[i]);
-                        acc[2 * i] += fl.x;
-                        acc[2 * i + 1] += fl.y;
+                    for (int i = 0; i < 4; ++i) {     // BF16 -> fp32 is a shift / a mask; packed fp32 add
+                        const float2 fl = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+                        const float2 r = __fadd2_rn(make_float2(acc[2 * i], acc[2 * i + 1]), fl);
+                        acc[2 * i] = r.x;
+                        acc[2 * i + 1] = r.y;
                     }
                 }
                 uint4 y;

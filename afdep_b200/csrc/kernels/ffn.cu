@@ -331,13 +331,16 @@ receive_kernel(const RankCtx c, const FfnWs ws, const ReceiveArgs r) {
     }
 }
 
+// acc[0..8) += the eight BF16 values of v, as exact fp32 additions.  A BF16 is the upper half
+// of an fp32, so unpacking is a shift and a mask, and sm_100's packed add does two lanes at once.
 __device__ __forceinline__ void acc_bf16x8(float* acc, const uint4& v) {
-    const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+    const unsigned w[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const float2 f = __bfloat1622float2(p[i]);
-        acc[2 * i] += f.x;
-        acc[2 * i + 1] += f.y;
+        const float2 x = make_float2(__uint_as_float(w[i] << 16), __uint_as_float(w[i] & 0xffff0000u));
+        const float2 r = __fadd2_rn(make_float2(acc[2 * i], acc[2 * i + 1]), x);
+        acc[2 * i] = r.x;
+        acc[2 * i + 1] = r.y;
     }
 }
 __device__ __forceinline__ uint4 pack_bf16x8(const float* acc) {
