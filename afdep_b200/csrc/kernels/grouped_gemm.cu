@@ -239,13 +239,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         break;
                     }
                     tc::fence_after_sync();
-#pragma unroll
-                    for (int ch = 0; ch < HN / 32; ++ch) {
-                        uint32_t v[32];
-                        tc::tmem_ld32(tmem + lane_base + (uint32_t)(buf * BN + half * HN + ch * 32), v);
-                        tc::tmem_ld_wait();
-                        // packed fp32 FMAs (two per instruction on sm_100) halve the promotion's issue slots
-                        const float2 s2 = make_float2(s, s);
+                    // Two register tiles in ping-pong: the tcgen05.ld of the next 32 columns is in
+                    // flight while the packed FMAs of the current 32 run (two fp32 lanes per
+                    // instruction on sm_100), so the promotion stays shorter than the MMAs it hides behind.
+                    const float2 s2 = make_float2(s, s);
+                    const uint32_t tsrc = tmem + lane_base + (uint32_t)(buf * BN + half * HN);
+                    uint32_t va[32], vb[32];
+                    auto promote = [&](const uint32_t (&v)[32], int ch) {
 #pragma unroll
                         for (int c = 0; c < 32; c += 2) {
                             const int i0 = kFp8 ? ch * 32 + c : 0;
@@ -254,6 +254,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                             acc[i0] = r.x;
                             acc[kFp8 ? i0 + 1 : 0] = r.y;
                         }
+                    };
+                    tc::tmem_ld32(tsrc, va);
+                    tc::tmem_ld_wait_on(va);
+#pragma unroll
+                    for (int ch = 0; ch < HN / 32; ch += 2) {
+                        tc::tmem_ld32(tsrc + (uint32_t)((ch + 1) * 32), vb);
+                        promote(va, ch);
+                        tc::tmem_ld_wait_on(vb);
+                        if (ch + 2 < HN / 32) tc::tmem_ld32(tsrc + (uint32_t)((ch + 2) * 32), va);
+                        promote(vb, ch + 1);
+                        if (ch + 2 < HN / 32) tc::tmem_ld_wait_on(va);
                     }
                     tc::fence_before_sync();
                     __syncwarp();
@@ -287,7 +298,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         uint32_t v0[32], v1[32];
                         tc::tmem_ld32(tbase + (uint32_t)(sub * 64), v0);
                         tc::tmem_ld32(tbase + (uint32_t)(sub * 64 + 32), v1);
-                        tc::tmem_ld_wait();
+                        tc::tmem_ld_wait_on(v0);
+                        tc::tmem_ld_wait_on(v1);
 #pragma unroll
                         for (int c = 0; c < 32; ++c) {
                             gt[c] = __uint_as_float(v0[c]);
@@ -318,7 +330,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     } else {
                         uint32_t v[32];
                         tc::tmem_ld32(tbase + (uint32_t)(ch * 32), v);
-                        tc::tmem_ld_wait();
+                        tc::tmem_ld_wait_on(v);
 #pragma unroll
                         for (int c = 0; c < 32; ++c) val[c] = __uint_as_float(v[c]);
                     }

@@ -45,14 +45,16 @@ def _exchange_once(buf, cfg, batches, *, tokens, read_host_counts=False):
             assert rec.recv_counts_host == exp.layout.aligned_counts
 
 
-def _roundtrip(rank, world, ffn, payload, hidden, tokens, experts, top_k):
+def _roundtrip(rank, world, ffn, payload, hidden, tokens, experts, top_k, heap_mode=None, role_aware=True):
     import torch.distributed as dist
 
     torch.cuda.set_device(rank)
     os.environ["NCCL_NVLS_ENABLE"] = "0"
     attn = world - ffn
-    cfg = Config(tokens, hidden, experts, top_k, ffn, attn, expert_alignment=16, payload=payload, gpu_timeout_s=10)
-    buf = Buffer(group=dist.group.WORLD, config=cfg)
+    cfg = Config(tokens, hidden, experts, top_k, ffn, attn, expert_alignment=16, payload=payload, gpu_timeout_s=10, role_aware=role_aware)
+    options = {"heap_mode": heap_mode} if heap_mode else {}
+    buf = Buffer(group=dist.group.WORLD, config=cfg, **options)
+    assert buf.transport._transport.heap_mode == (heap_mode or buf.transport._transport.heap_mode)
     assert buf.transport._transport.heap_mode in ("vmm", "ipc")
     for epoch in range(3):
         batches = [synthetic.random_batch(cfg, tokens - 11 * a, seed=17 * epoch + a, skip_fraction=0.05) for a in range(attn)]
@@ -104,6 +106,12 @@ def _roundtrip(rank, world, ffn, payload, hidden, tokens, experts, top_k):
 @pytest.mark.parametrize("payload", ["bf16", "fp8"])
 def test_two_gpus_one_attention_one_ffn(payload):
     run_ranks(_roundtrip, 2, 1, payload, 1024, 256, 16, 4, timeout=600)
+
+
+@pytest.mark.multigpu(2)
+def test_two_gpus_cuda_ipc_heap_and_generic_receive_bound():
+    """The cudaIpc fallback of the symmetric heap, with the reference's generic (role_aware=False) bound."""
+    run_ranks(_roundtrip, 2, 1, "bf16", 512, 128, 8, 2, "ipc", False, timeout=600)
 
 
 @pytest.mark.multigpu(4)
