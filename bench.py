@@ -69,7 +69,7 @@ def topology(n: int, config: str) -> tuple[int, int]:
 
 class ClockSampler:
     """SM clock and throttle reasons while the timed region runs.  Read-only NVML queries from
-    a background thread (every 2 ms); falls back to one `nvidia-smi` query if NVML is missing."""
+    a background thread (about every millisecond); falls back to one `nvidia-smi` query if NVML is missing."""
 
     REASONS = {
         "hw_slowdown": 0x8,
@@ -138,13 +138,15 @@ def reference_arm(args) -> None:
     rank = int(os.environ.get("RANK", "0"))
     reason = None
     ref = os.path.join(ROOT, "baseline", "_ref")
-    if args.gpus < 2:
-        reason = "the reference needs at least two ranks (afdep/deepep.py:218-221); there is no 1-GPU mode"
-    elif not os.path.isdir(os.path.join(ref, "afdep")):
+    if not os.path.isdir(os.path.join(ref, "afdep")):
         reason = (
             "closed on this pool: the reference's source calls a batched-memcpy CUDA entry point that is closed here "
             "(csrc/elastic/buffer.hpp:439), so its install under baseline/_ref cannot be carried to the GPU box"
         )
+        if args.gpus < 2:
+            reason += "; it also has no 1-GPU mode (needs at least two ranks, afdep/deepep.py:218-221)"
+    elif args.gpus < 2:
+        reason = "the reference needs at least two ranks (afdep/deepep.py:218-221); there is no 1-GPU mode"
     else:
         probe = (
             "import sys; sys.path.insert(0, %r); from afdep._build import load_deepep; load_deepep(); print('built')" % ref
