@@ -176,3 +176,53 @@ def _nccl_baseline(rank, world, ffn, payload):
 def test_nccl_baseline_transport_matches_oracle(payload):
     """The baseline the kernels are compared with must itself be a correct exchange."""
     run_ranks(_nccl_baseline, 2, 1, payload, timeout=600)
+
+
+def _stress(rank, world, ffn, steps):
+    """Many back-to-back exchanges with changing token counts and routes, no host sync in between,
+    two Buffers alive at once: epochs, flags and heap reuse must hold up."""
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    attn = world - ffn
+    cfgs = [Config(256, 512, 8 * ffn, 4, ffn, attn, expert_alignment=16, payload=p, gpu_timeout_s=20) for p in ("bf16", "fp8")]
+    bufs = [Buffer(group=dist.group.WORLD, config=c) for c in cfgs]
+    gen = torch.Generator().manual_seed(1234)          # same sequence on every rank
+    pending = []
+    for step in range(steps):
+        which = step % 2
+        buf, cfg = bufs[which], cfgs[which]
+        counts = [int(torch.randint(0, 257, (1,), generator=gen)) for _ in range(attn)]
+        skip = float(torch.rand(1, generator=gen)) * 0.5
+        batches = [synthetic.random_batch(cfg, counts[a], seed=step * 16 + a, skip_fraction=skip) for a in range(attn)]
+        if buf.role == "attention":
+            x, ids, w, scale = _to_dev(batches[buf.role_rank])
+            buf.source_dispatch(x, ids, w, scale, bucket=256)
+            out = buf.source_collect()
+            pending.append((out, cfg, batches[buf.role_rank]))
+        else:
+            rec = buf.worker_receive(bucket=256)
+            rows = oracle.synthetic_expert_rows(cfg, buf.role_rank, rec.recv_x, rec.recv_scale, rec.recv_topk_weights, rec.recv_count_psum)
+            buf.worker_reply(rows, rec.receipt)
+        if step % 25 == 24:                            # verify in bursts, so that launches queue up in between
+            torch.cuda.synchronize()
+            for b in bufs:
+                b.check()
+            for out, c, batch in pending:
+                expect = oracle.expected_combine(c, oracle.SourceBatch(*batch))
+                assert torch.equal(out.cpu().float(), expect.float())
+            pending.clear()
+    torch.cuda.synchronize()
+    dist.barrier()
+    for b in bufs:
+        b.close()
+
+
+@pytest.mark.multigpu(2)
+def test_two_gpus_stress_two_buffers_changing_shapes():
+    run_ranks(_stress, 2, 1, 150, timeout=900)
+
+
+@pytest.mark.multigpu(4)
+def test_four_gpus_stress_two_buffers_changing_shapes():
+    run_ranks(_stress, 4, 2, 100, timeout=900)
