@@ -23,13 +23,16 @@ struct RankCtx {
     int* poison;     // device word
     long long budget;   // clock64 ticks a wait may spin
     int bounds_check;   // verify computed rows/slots before use
-    // Optional device buffer [4 kernels][kTraceCtas][4] of %globaltimer stamps (ns): start,
-    // end of the kernel's first phase, end of its main loop, exit.  Null when tracing is off.
+    // Optional device buffer [kTraceRows][kTraceCtas][4] of %globaltimer stamps (ns).  Rows
+    // dispatch/receive/reply/collect: start, end of the kernel's first phase, end of its main
+    // loop, unused.  Row layout (inside dispatch): after set-up, after ranking, after the
+    // look-back, after the fix-up.  Null when tracing is off.
     unsigned long long* trace;
 };
 
 constexpr int kTraceCtas = 320;
-enum TraceKernel : int { kTraceDispatch = 0, kTraceReceive = 1, kTraceReply = 2, kTraceCollect = 3 };
+enum TraceKernel : int { kTraceDispatch = 0, kTraceReceive = 1, kTraceReply = 2, kTraceCollect = 3, kTraceLayout = 4 };
+constexpr int kTraceRows = 5;
 
 // Device-local scratch of an attention rank (not visible to peers).
 struct AttnWs {

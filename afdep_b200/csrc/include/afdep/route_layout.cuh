@@ -46,6 +46,7 @@ struct RouteLayoutJob {
     int* lb;                     // smem [F + E]: sum over earlier CTAs (zero in redundant mode)
     int* local;                  // smem [tokens][2K + F] (e, pos, slot) or null
     int redundant;               // 1: every CTA ranks all tokens
+    unsigned long long* trace;   // optional time stamps (row 4 of the trace buffer), or null
 };
 
 __host__ __device__ __forceinline__ int route_layout_scratch_ints(int warps, int ncols) { return (warps + 2) * ncols; }
@@ -94,6 +95,7 @@ __device__ __forceinline__ bool route_layout_phase(const RouteLayoutJob& j, cons
     }
     if (tid == 0) s_dead = 0;
     __syncthreads();
+    trace_stamp(j.trace, 4, 0);
 
     {
         const int tpb = 32 / K;                 // tokens handled per warp step
@@ -178,6 +180,7 @@ __device__ __forceinline__ bool route_layout_phase(const RouteLayoutJob& j, cons
         }
     }
     __syncthreads();
+    trace_stamp(j.trace, 4, 1);
 
     // exclusive scan over the CTA's warps; in distributed mode publish the CTA aggregate
     for (int col = tid; col < ncols; col += blockDim.x) {
@@ -228,22 +231,31 @@ __device__ __forceinline__ bool route_layout_phase(const RouteLayoutJob& j, cons
         }
     }
     __syncthreads();
+    trace_stamp(j.trace, 4, 2);
 
     // fix-up: warp-local ranks -> global pos / slot, for the tokens this warp ranked
     {
         const int* my = wh + warp * ncols;
         const int* lb = j.lb;
         if (j.local != nullptr) {
-            const int cnt = (w1 - w0) * LW;
-            for (int i = lane; i < cnt; i += 32) {
-                int* row = j.local + (size_t)(w0 - r0 + i / LW) * LW;
-                const int c = i % LW;
-                if (c >= K && c < 2 * K) {
-                    const int e = row[c - K];
-                    if (e >= 0) row[c] += my[F + e] + lb[F + e];
-                } else if (c >= 2 * K) {
-                    const int f = c - 2 * K;
-                    if (row[c] >= 0) row[c] += my[f] + lb[f];
+            // lanes cover the pos and slot words of several tokens per step; the lane -> (token,
+            // word) split is computed once, so the loop itself has no divisions
+            const int per = LW - K;                          // words to fix per token
+            const int tps = per <= 32 ? 32 / per : 1;        // tokens per step
+            const int tsub = per <= 32 ? lane / per : 0;
+            const int c0 = K + (per <= 32 ? lane - tsub * per : lane);
+            if (tsub < tps) {
+                for (int t = w0 + tsub; t < w1; t += tps) {
+                    int* row = j.local + (size_t)(t - r0) * LW;
+                    for (int c = c0; c < LW; c += (per <= 32 ? LW : 32)) {
+                        if (c < 2 * K) {
+                            const int e = row[c - K];
+                            if (e >= 0) row[c] += my[F + e] + lb[F + e];
+                        } else {
+                            const int f = c - 2 * K;
+                            if (row[c] >= 0) row[c] += my[f] + lb[f];
+                        }
+                    }
                 }
             }
         } else {
@@ -263,6 +275,7 @@ __device__ __forceinline__ bool route_layout_phase(const RouteLayoutJob& j, cons
         }
     }
     __syncthreads();
+    trace_stamp(j.trace, 4, 3);
 
     // the shared-memory table is final: write the global copies of the tokens this CTA owns
     if (j.local != nullptr) {

@@ -88,6 +88,7 @@ dispatch_kernel(const RankCtx c, const AttnWs ws, const DispatchArgs a, const Di
     job.lb = lb;
     job.local = local;
     job.redundant = plan.redundant;
+    job.trace = c.trace;
     const bool alive = route_layout_phase(job, wc);
     // Phase 2 walks the tokens round-robin over all CTAs (so records reach the receivers in
     // slot order).  When the layout is distributed, a token's routing words were produced by

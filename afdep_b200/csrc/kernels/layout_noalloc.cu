@@ -51,6 +51,7 @@ route_layout_noalloc_kernel(const long long* __restrict__ ids, int T, int K, int
     job.lb = job.tot + ncols;
     job.local = nullptr;
     job.redundant = 0;
+    job.trace = nullptr;
     int* tot = job.tot;
     int* lb = job.lb;
     const bool ok = afdep::route_layout_phase(job, wc);

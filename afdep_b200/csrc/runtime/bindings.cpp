@@ -363,7 +363,7 @@ public:
         return out;
     }
 
-    // Per-CTA time stamps of the exchange kernels: int64 [4 kernels][kTraceCtas][4] in
+    // Per-CTA time stamps of the exchange kernels: int64 [kTraceRows][kTraceCtas][4] in
     // nanoseconds of the GPU's global timer; pass enable=false to switch tracing off again.
     torch::Tensor trace(bool enable) {
         if (!enable) {
@@ -371,7 +371,7 @@ public:
             return trace_;
         }
         if (!trace_.defined())
-            trace_ = torch::zeros({4, kTraceCtas, 4}, torch::TensorOptions().dtype(torch::kInt64).device(torch::kCUDA, device_));
+            trace_ = torch::zeros({kTraceRows, kTraceCtas, 4}, torch::TensorOptions().dtype(torch::kInt64).device(torch::kCUDA, device_));
         ctx_.trace = reinterpret_cast<unsigned long long*>(trace_.data_ptr<int64_t>());
         return trace_;
     }
