@@ -37,6 +37,8 @@ constexpr int kRedundantEntries = 4096;     // every CTA ranks all tokens up to 
 // How a launch is laid out; computed on the host, identical for every CTA.
 struct DispatchPlan {
     int ctas, warps, nb, smem_bytes;
+    int data_warps;      // warps [0, data_warps) push records, warp data_warps releases flags, the
+                         // rest only help with the layout phase
     int route_rows;      // rows of the shared-memory routing table, 0: keep it in global memory
     int redundant;       // 1: every CTA ranks all tokens (no traffic between CTAs)
     int route_bytes;     // bytes reserved for the table
@@ -52,7 +54,7 @@ dispatch_kernel(const RankCtx c, const AttnWs ws, const DispatchArgs a, const Di
     constexpr int L = NB - 2;     // how many tokens the hand-off lags behind the stores
     extern __shared__ __align__(128) unsigned char smem[];
     const Geometry& g = c.g;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, NW = blockDim.x >> 5;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int G = gridDim.x, cta = blockIdx.x;
     const int F = g.ffn, K = g.top_k, E = g.num_experts, EL = g.experts_local, C = g.capacity;
     const int ncols = F + E, LW = 2 * K + F;
@@ -102,8 +104,9 @@ dispatch_kernel(const RankCtx c, const AttnWs ws, const DispatchArgs a, const Di
     ptx::fence_proxy_async_smem();
 
     // ------------------------------------------------------------------ phase 2: push
-    // Warps [0, ND) move data; the last warp releases counts and arrival flags.
-    const int ND = NW - 1;
+    // Warps [0, ND) move data, warp ND releases counts and arrival flags; any further warps only
+    // took part in the layout phase (more hands there shorten the part every exchange waits on).
+    const int ND = plan.data_warps;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem);
     int* done_cnt = reinterpret_cast<int*>(smem + kBarBytes - 128);   // [ND] tokens completed per data warp
     unsigned char* bufs = overlay + (size_t)warp * NB * g.rec_bytes;
@@ -252,7 +255,7 @@ dispatch_kernel(const RankCtx c, const AttnWs ws, const DispatchArgs a, const Di
             }
             ptx::st_release_cta_shared(&done_cnt[warp], ok ? n_w : -1);
         }
-    } else {
+    } else if (warp == ND) {
         // Flag warp.  First, in the CTA that holds the source's totals, the count "all-to-all":
         // per-expert counts and the record count go to every FFN rank ahead of the payload flags.
         if (cta == G - 1 && alive) {
@@ -352,12 +355,18 @@ DispatchPlan plan_dispatch(const Geometry& g, int tokens, int num_sms) {
     data_warps = (room - p.route_bytes) / (p.nb * g.rec_bytes);
     if (data_warps > kMaxWarps - 1) data_warps = kMaxWarps - 1;
     if (data_warps < 1) data_warps = 1;
-    int warps = data_warps + 1;          // plus the flag warp
-    // The layout histograms share the overlay with the record buffers.
-    while (warps > 2 && p.route_bytes + p.totals_bytes + warps * ncols * 4 > avail) --warps;
+    p.data_warps = data_warps;
+    // Always a full block: the warps beyond the data warps and the flag warp join the layout
+    // phase.  The layout histograms share the overlay with the record buffers.
+    int warps = kMaxWarps;
+    while (warps > data_warps + 1 && p.route_bytes + p.totals_bytes + warps * ncols * 4 > avail) --warps;
+    while (warps > 2 && p.route_bytes + p.totals_bytes + warps * ncols * 4 > avail) {
+        --warps;
+        p.data_warps = warps - 1;
+    }
     p.warps = warps;
     const int p1 = warps * ncols * 4;
-    const int p2 = (warps - 1) * p.nb * g.rec_bytes;
+    const int p2 = p.data_warps * p.nb * g.rec_bytes;
     p.smem_bytes = kBarBytes + p.route_bytes + p.totals_bytes + (p1 > p2 ? p1 : p2);
     return p;
 }
