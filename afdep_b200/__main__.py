@@ -62,6 +62,7 @@ def report(build: bool) -> dict:
             out["native_library_built"] = True
             out["native_module"] = module.__name__
             out["native_max_ranks"] = int(module.max_ranks)
+            out["native_build"] = dict(module.build_info())
             import torch
 
             if torch.cuda.is_available():

@@ -75,6 +75,7 @@ struct ReceiveArgs {
     float* recv_w;          // [rows_cap]
     int* recv_src;          // [rows_cap][2]: source attention rank, source token
     int* psum;              // [experts_local] end row of every expert segment
+    long long* expert_stats;  // optional [experts_local]: running total of rows received per expert
     int rows_cap;
     int layout_ready;       // 1: launch_ffn_layout already ran for this exchange
     int write_host_counts;  // layout kernel only

@@ -113,6 +113,7 @@ __device__ void publish_layout(const RankCtx& c, const FfnWs& ws, const ReceiveA
     for (int el = threadIdx.x; el < EL; el += blockDim.x) {
         const int end = L.start[el] + L.tot[el];
         if (r.psum) r.psum[el] = end;
+        if (r.expert_stats) r.expert_stats[el] += L.tot[el];     // one CTA publishes per exchange
         ws.ends[el] = end;
     }
     for (int i = threadIdx.x; i < A * EL; i += blockDim.x) ws.row_base[i] = L.row_base[i];

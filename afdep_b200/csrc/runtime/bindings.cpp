@@ -26,6 +26,7 @@
 #include "afdep/route_layout_api.h"
 #include "driver.hpp"
 #include "heap.hpp"
+#include "stream_memops.hpp"
 
 namespace py = pybind11;
 
@@ -211,6 +212,7 @@ public:
         auto psum = torch::empty({EL}, dev.dtype(torch::kInt32));
         ReceiveArgs r{};
         r.psum = psum.data_ptr<int>();
+        r.expert_stats = expert_stats_.defined() ? reinterpret_cast<long long*>(expert_stats_.data_ptr<int64_t>()) : nullptr;
         std::vector<int64_t> host_counts;
         int64_t rows = rows_bound;
         if (read_host_counts) {
@@ -272,6 +274,18 @@ public:
         return py::make_tuple(recv_x, scale_obj, recv_w, psum, host_counts, recv_src);
     }
 
+    // Running total of rows received per local expert, summed on the device by the receive
+    // path from now on (int64 [experts_local]); the tensor stays valid until destroy().  The
+    // reference offers the same counter as an optional dispatch argument
+    // (csrc/elastic/buffer.hpp:740-748).
+    torch::Tensor enable_expert_stats() {
+        TORCH_CHECK(!destroyed_, "buffer is closed");
+        TORCH_CHECK(is_ffn_, "expert statistics are kept on FFN ranks");
+        if (!expert_stats_.defined())
+            expert_stats_ = torch::zeros({geo_.experts_local}, torch::TensorOptions().dtype(torch::kInt64).device(torch::kCUDA, device_));
+        return expert_stats_;
+    }
+
     void worker_reply(const torch::Tensor& rows) {
         live();
         TORCH_CHECK(is_ffn_, "worker_reply runs on FFN ranks");
@@ -330,8 +344,37 @@ public:
         rt_check(launch_allgather_push(ctx_, aux_seq(), t.data_ptr(), bytes, (size_t)aux_slot_bytes(), aux_ctas(bytes), stream()), "all-gather launch");
         ++launches_;
     }
+    // The same all-gather without an SM: one copy-engine transfer per peer, then one batched
+    // stream memory operation that writes this gather's number into every peer's flag word.
+    // The number comes from a host-side count of completed gathers, so this form cannot be
+    // captured into a CUDA graph; once a capture has contained the kernel form, the count is
+    // re-read from the device (one stream synchronisation) before every use.
+    void allgather_push_copy(const torch::Tensor& t) {
+        live();
+        const size_t bytes = check_aux_tensor(t);
+        cudaStream_t s = stream();
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        rt_check(cudaStreamIsCapturing(s, &cap), "cudaStreamIsCapturing");
+        TORCH_CHECK(cap == cudaStreamCaptureStatusNone, "the copy-engine all-gather cannot be captured into a CUDA graph");
+        if (gather_in_graph_) {     // replays advance the device count behind the host's back
+            rt_check(cudaStreamSynchronize(s), "cudaStreamSynchronize");
+            rt_check(cudaMemcpy(&gathers_done_, aux_seq().gather, sizeof(unsigned), cudaMemcpyDeviceToHost), "cudaMemcpy");
+        }
+        const size_t slot = (size_t)aux_slot_bytes();
+        std::vector<StreamWrite32> flags;
+        for (int p = 0; p < geo_.world; ++p) {
+            char* aux = ctx_.peer[p] + geo_.aux_off;
+            rt_check(cudaMemcpyAsync(aux + kAuxSignalBytes + (size_t)rank_ * slot, t.data_ptr(), bytes, cudaMemcpyDeviceToDevice, s),
+                     "all-gather peer copy");
+            flags.push_back({aux + sizeof(uint32_t) * (size_t)rank_, gathers_done_ + 1u});
+        }
+        stream_write32_batch(s, flags);
+    }
     void allgather_wait() {
         live();
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        rt_check(cudaStreamIsCapturing(stream(), &cap), "cudaStreamIsCapturing");
+        if (cap == cudaStreamCaptureStatusNone) ++gathers_done_; else gather_in_graph_ = true;
         rt_check(launch_allgather_wait(ctx_, aux_seq(), stream()), "all-gather wait launch");
         ++launches_;
     }
@@ -390,6 +433,7 @@ public:
         scratch_ = torch::Tensor();
         agg_ = torch::Tensor();
         trace_ = torch::Tensor();
+        expert_stats_ = torch::Tensor();
         heap_->release();
         if (host_block_) cudaFreeHost(host_block_);
         host_block_ = nullptr;
@@ -443,6 +487,9 @@ private:
     void* host_block_ = nullptr;
     torch::Tensor flags_, scratch_, agg_, trace_;
     int64_t host_seq_ = 0, launches_ = 0;
+    torch::Tensor expert_stats_;      // optional running per-expert row totals
+    unsigned gathers_done_ = 0;       // all-gathers waited for outside graph capture
+    bool gather_in_graph_ = false;    // an all-gather wait has been captured into a graph
 };
 
 // Deterministic routing layout of one source (see kernels/layout.cu).  Returns
@@ -578,6 +625,23 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.doc() = "afdep_b200 native runtime (sm_100a)";
     m.attr("max_ranks") = afdep::kMaxRanks;
     m.def("vmm_supported", [](int device) { return afdep::SymmetricHeap::vmm_supported(device); });
+    // What this library was compiled as and against; the doctor prints it.  Counterpart of the
+    // reference module's version and architecture queries (csrc/python_api.cpp:26-56).
+    m.def("build_info", [] {
+        py::dict d;
+        int runtime = 0, driver = 0;
+        cudaRuntimeGetVersion(&runtime);
+        if (cudaDriverGetVersion(&driver) != cudaSuccess) cudaGetLastError();
+        d["arch"] = "sm_100a";
+        d["cuda_compiled"] = CUDART_VERSION;
+        d["cuda_runtime"] = runtime;
+        d["cuda_driver"] = driver;
+        d["topk_index_dtype"] = "int64";
+        d["max_ranks"] = afdep::kMaxRanks;
+        d["trace_ctas"] = afdep::kTraceCtas;
+        d["stream_memops"] = true;
+        return d;
+    });
     m.def("grouped_gemm", &afdep::grouped_gemm, py::arg("a"), py::arg("w"), py::arg("ends"), py::arg("alignment"),
           py::arg("swiglu") = false, py::arg("row_scale") = py::none(), py::arg("a_scale") = py::none(),
           py::arg("w_scale") = py::none(), py::arg("out") = py::none(), py::arg("ctas") = 0);
@@ -611,6 +675,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("aux_slot_bytes", &NativeBuffer::aux_slot_bytes)
         .def("aux_view", &NativeBuffer::aux_view)
         .def("allgather_push", &NativeBuffer::allgather_push)
+        .def("enable_expert_stats", &NativeBuffer::enable_expert_stats)
+        .def("allgather_push_copy", &NativeBuffer::allgather_push_copy)
         .def("allgather_wait", &NativeBuffer::allgather_wait)
         .def("p2p_send", &NativeBuffer::p2p_send)
         .def("p2p_recv", &NativeBuffer::p2p_recv)

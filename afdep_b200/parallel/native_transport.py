@@ -79,6 +79,9 @@ class NativeTransport:
         self.num_sms = num_sms
         self.is_ffn = control.rank < config.ffn_ranks
         self._empty = None
+        # Optional running total of rows received per local expert (FFN ranks), accumulated on
+        # the device by the receive kernels; read it with ``stats()`` or as ``expert_stats``.
+        self.expert_stats = self._nb.enable_expert_stats() if options.get("expert_stats") and self.is_ffn else None
         # Optional dedicated high-priority stream for the exchange kernels, ordered against the
         # caller's current stream with events on both sides of every call (what the reference
         # always does, csrc/elastic/buffer.hpp:476-534).  Off by default: staying on the current
@@ -195,6 +198,7 @@ class NativeTransport:
             "launches": int(self._nb.launches()),
             "num_sms": int(self._nb.resolved_num_sms()),
             "status": dict(self._nb.status()),
+            **({"expert_rows_received": self.expert_stats.tolist()} if self.expert_stats is not None else {}),
         }
 
     # ---- role operations --------------------------------------------------------------

@@ -33,14 +33,24 @@ class HeapPrimitives:
         return int(self._nb.aux_slot_bytes())
 
     # ---- all-gather ---------------------------------------------------------------------
-    def all_gather_start(self, tensor: torch.Tensor):
+    def all_gather_start(self, tensor: torch.Tensor, *, engine: str = "sm"):
         """Push ``tensor`` into every peer's slot for this rank.  Returns a handle whose
-        ``wait()`` yields the ``[world_size, *tensor.shape]`` view of the gathered data."""
-        self._nb.allgather_push(tensor)
+        ``wait()`` yields the ``[world_size, *tensor.shape]`` view of the gathered data.
+
+        ``engine="sm"`` copies with a kernel (graph-capturable).  ``engine="copy"`` uses one
+        copy-engine transfer per peer and a batched stream memory operation for the flags, so
+        no SM is occupied while compute kernels run; it is eager-only.  All ranks may choose
+        independently: the flags and the bounded wait are the same."""
+        if engine == "sm":
+            self._nb.allgather_push(tensor)
+        elif engine == "copy":
+            self._nb.allgather_push_copy(tensor)
+        else:
+            raise ValueError("engine must be 'sm' or 'copy'")
         return _GatherHandle(self, tensor.shape, tensor.dtype, tensor.numel() * tensor.element_size())
 
-    def all_gather(self, tensor: torch.Tensor) -> torch.Tensor:
-        return self.all_gather_start(tensor).wait()
+    def all_gather(self, tensor: torch.Tensor, *, engine: str = "sm") -> torch.Tensor:
+        return self.all_gather_start(tensor, engine=engine).wait()
 
     # ---- neighbour send / recv -------------------------------------------------------------
     def send(self, tensor: torch.Tensor, dst: int) -> None:

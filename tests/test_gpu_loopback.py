@@ -248,3 +248,24 @@ def test_dedicated_comm_stream_option():
             run_and_check(world, cfg, batches)
     finally:
         world.close()
+
+
+def test_expert_stats_accumulate_on_the_device():
+    """Optional running totals of rows received per local expert, eager and host-count paths."""
+    cfg = Config(64, 256, 16, 4, 2, 2, expert_alignment=8)
+    world = make_world(cfg, expert_stats=True)
+    try:
+        want = torch.zeros(cfg.num_experts, dtype=torch.int64)
+        for epoch, host in enumerate((False, True, False)):
+            batches = [synthetic.random_batch(cfg, 64 - 9 * a, seed=5 * epoch + a, skip_fraction=0.1) for a in range(2)]
+            run_and_check(world, cfg, batches, read_host_counts=host, exact=False)
+            for b in batches:
+                ids = b[1][b[1] >= 0]
+                want += torch.bincount(ids, minlength=cfg.num_experts)
+        el = cfg.experts_per_rank
+        for f in range(cfg.ffn_ranks):
+            got = world.buffers[f].stats()["expert_rows_received"]
+            assert got == want[f * el : (f + 1) * el].tolist()
+        assert "expert_rows_received" not in world.buffers[cfg.ffn_ranks].stats()      # attention rank
+    finally:
+        world.close()

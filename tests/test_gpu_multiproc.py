@@ -226,3 +226,47 @@ def test_two_gpus_stress_two_buffers_changing_shapes():
 @pytest.mark.multigpu(4)
 def test_four_gpus_stress_two_buffers_changing_shapes():
     run_ranks(_stress, 4, 2, 100, timeout=900)
+
+
+def _primitives(rank, world):
+    """All-gather (kernel and copy-engine forms), ring send/recv and row fetch across real GPUs."""
+    import torch.distributed as dist
+
+    from afdep_b200.parallel.primitives import HeapPrimitives
+
+    torch.cuda.set_device(rank)
+    cfg = Config(8, 256, 8 * (world // 2), 2, world // 2, world - world // 2, gpu_timeout_s=10)
+    buf = Buffer(group=dist.group.WORLD, config=cfg, aux_bytes=8 << 20)
+    prims = HeapPrimitives(buf)
+
+    def part(r, rnd):          # every rank can rebuild every other rank's contribution
+        g = torch.Generator().manual_seed(100 * rnd + r)
+        return torch.randn(64, 128, generator=g).bfloat16()
+
+    for rnd, engine in enumerate(("sm", "copy", "copy", "sm", "copy")):
+        got = prims.all_gather(part(rank, rnd).cuda(), engine=engine)
+        torch.cuda.synchronize()
+        assert torch.equal(got.cpu(), torch.stack([part(r, rnd) for r in range(world)])), f"gather {rnd} ({engine})"
+        prims.barrier()        # nobody overwrites a slot its peers may still be reading
+    for step in range(3):
+        prims.send(part(rank, 50 + step).cuda(), (rank + 1) % world)
+        out = torch.empty(64, 128, device="cuda", dtype=torch.bfloat16)
+        prims.recv(out, (rank - 1) % world)
+        torch.cuda.synchronize()
+        assert torch.equal(out.cpu(), part((rank - 1) % world, 50 + step))
+    rows, width = 32, 128
+    prims.table_shard(rows, width, torch.bfloat16).copy_(part(rank, 99)[:rows].cuda())
+    prims.barrier()
+    idx = torch.tensor([0, rows * world - 1, rows, 5, rows + 7], device="cuda")
+    got = prims.fetch_rows(idx, rows, width, torch.bfloat16)
+    torch.cuda.synchronize()
+    table = torch.cat([part(r, 99)[:rows] for r in range(world)])
+    assert torch.equal(got.cpu(), table[idx.cpu()])
+    buf.check()
+    dist.barrier()
+    buf.close()
+
+
+@pytest.mark.multigpu(2)
+def test_two_gpus_heap_primitives_both_gather_engines():
+    run_ranks(_primitives, 2, timeout=600)

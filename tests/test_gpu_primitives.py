@@ -36,6 +36,23 @@ def test_all_gather(world):
         b.check()
 
 
+def test_all_gather_copy_engine_and_mixed(world):
+    """Copy-engine pushes with stream-ordered flag writes; ranks may mix the two engines, and
+    the two forms may alternate from one gather to the next."""
+    prims = [HeapPrimitives(b) for b in world.buffers]
+    for rnd, engines in enumerate((["copy"] * 4, ["copy", "sm", "copy", "sm"], ["sm"] * 4, ["copy"] * 4)):
+        parts = [torch.randn(40, 64, device="cuda").bfloat16() + rnd for _ in range(4)]
+        handles = [p.all_gather_start(t, engine=e) for p, t, e in zip(prims, parts, engines)]
+        for h in handles:
+            got = h.wait()
+            torch.cuda.synchronize()
+            assert torch.equal(got, torch.stack(parts))
+    with pytest.raises(ValueError):
+        prims[0].all_gather_start(parts[0], engine="dma")
+    for b in world.buffers:
+        b.check()
+
+
 def test_send_recv_ring_with_credits(world):
     prims = [HeapPrimitives(b) for b in world.buffers]
     n = len(prims)
