@@ -25,14 +25,20 @@ struct RankCtx {
     int bounds_check;   // verify computed rows/slots before use
     // Optional device buffer [kTraceRows][kTraceCtas][4] of %globaltimer stamps (ns).  Rows
     // dispatch/receive/reply/collect: start, end of the kernel's first phase, end of its main
-    // loop, unused.  Row layout (inside dispatch): after set-up, after ranking, after the
-    // look-back, after the fix-up.  Null when tracing is off.
+    // loop, and (dispatch) counts released to the FFN ranks / (receive) counts of all sources seen.  Row layout (inside dispatch): after set-up, after ranking, after the
+    // look-back, after the fix-up.  Rows "first": progress of warp 0's first record (receive) or
+    // token (collect) in every CTA that has one.  Null when tracing is off.
     unsigned long long* trace;
 };
 
 constexpr int kTraceCtas = 320;
-enum TraceKernel : int { kTraceDispatch = 0, kTraceReceive = 1, kTraceReply = 2, kTraceCollect = 3, kTraceLayout = 4 };
-constexpr int kTraceRows = 5;
+enum TraceKernel : int {
+    kTraceDispatch = 0, kTraceReceive = 1, kTraceReply = 2, kTraceCollect = 3, kTraceLayout = 4,
+    // First record / token of warp 0 in every CTA that has one:
+    kTraceReceiveFirst = 5,   // arrival flag seen, record landed in smem, stores committed, stores complete
+    kTraceCollectFirst = 6,   // reply flags seen, rows landed in smem, output stored, unused
+};
+constexpr int kTraceRows = 7;
 
 // Device-local scratch of an attention rank (not visible to peers).
 struct AttnWs {

@@ -42,8 +42,7 @@ struct Geometry {
     int meta_off;       // offset of the metadata inside a record
 
     // FFN-rank heap
-    size_t f_cnt;        // int32 [attn][experts_local + 4]: counts, then records sent
-    size_t f_cnt_flag;   // uint32 [attn] (one 128-byte line each)
+    size_t f_cnt;        // uint64 [attn][experts_local + 4]: (epoch << 32 | count) per expert, then records sent
     size_t f_slot_flag;  // uint32 [attn][capacity]
     size_t f_stage;      // records [attn][capacity]
     size_t f_reply;      // bf16 rows [attn][capacity]
@@ -85,9 +84,7 @@ inline Geometry make_geometry(int ffn, int attn, int hidden, int top_k, int num_
 
     size_t o = base;
     g.f_cnt = o;
-    o = align_sz(o + (size_t)attn * (g.experts_local + 4) * 4, 256);
-    g.f_cnt_flag = o;
-    o = align_sz(o + (size_t)attn * 128, 256);
+    o = align_sz(o + (size_t)attn * (g.experts_local + 4) * 8, 256);
     g.f_slot_flag = o;
     o = align_sz(o + (size_t)attn * capacity * 4, 256);
     g.f_stage = o;

@@ -63,6 +63,11 @@ __device__ __forceinline__ void trace_stamp(unsigned long long* trace, int kerne
         trace[((size_t)kernel * 320 + blockIdx.x) * 4 + stamp] = ptx::globaltimer_ns();
 }
 
+// The same from whichever single thread the caller picked.
+__device__ __forceinline__ void trace_stamp_here(unsigned long long* trace, int kernel, int stamp) {
+    if (trace != nullptr && blockIdx.x < 320) trace[((size_t)kernel * 320 + blockIdx.x) * 4 + stamp] = ptx::globaltimer_ns();
+}
+
 __device__ __forceinline__ void poison(const WaitCtx& w) { atomicExch(w.poison + kPoison, 1); }
 __device__ __forceinline__ bool poisoned(const WaitCtx& w) { return *(volatile int*)(w.poison + kPoison) != 0; }
 

@@ -48,7 +48,7 @@ collect_kernel(const RankCtx c, const AttnWs ws, unsigned char* __restrict__ out
     trace_stamp(c.trace, kTraceCollect, 0);
     const int nvec = g.hidden / 8;
     unsigned it = 0;
-    for (int t = cta * NW + warp; t < T; t += G * NW) {
+    for (int t = warp * G + cta; t < T; t += G * NW) {      // consecutive tokens on consecutive CTAs
         const int slot = (lane < F) ? ws.tok_slot[(size_t)t * F + lane] : -1;
         const unsigned mask = __ballot_sync(ptx::kFullMask, slot >= 0);
         unsigned char* dst = out + (size_t)t * g.row_bytes;
@@ -69,6 +69,7 @@ collect_kernel(const RankCtx c, const AttnWs ws, unsigned char* __restrict__ out
             }
         }
         if (!__all_sync(ptx::kFullMask, ok)) break;
+        if (it == 0) trace_stamp(c.trace, kTraceCollectFirst, 0);
         const int nrows = __popc(mask);
         if (lane == 0) {
             ptx::fence_proxy_async_global();
@@ -90,6 +91,7 @@ collect_kernel(const RankCtx c, const AttnWs ws, unsigned char* __restrict__ out
             }
             break;
         }
+        if (it == 0) trace_stamp(c.trace, kTraceCollectFirst, 1);
         ++it;
         if (nrows == 1) {
             for (int v = lane; v < nvec; v += 32)
@@ -116,6 +118,7 @@ collect_kernel(const RankCtx c, const AttnWs ws, unsigned char* __restrict__ out
             }
         }
         __syncwarp();   // every lane is done with the buffer before the next bulk load lands
+        if (it == 1) trace_stamp(c.trace, kTraceCollectFirst, 2);
     }
 
     __syncthreads();
@@ -165,9 +168,10 @@ LaunchShape collect_shape(const Geometry& g, int tokens, int num_sms, int max_sm
     int warps = (max_smem - kBarBytes) / (max_rows * g.row_bytes);
     if (warps > kMaxWarps) warps = kMaxWarps;
     if (warps < 1) warps = 1;
+    // Few tokens: one per CTA rather than a full CTA of warps on a few SMs, so that every
+    // token's rows come in through a different SM's copy engine.
     int ctas = num_sms;
-    int want = (tokens + warps - 1) / warps;
-    if (want < 1) want = 1;
+    int want = tokens < 1 ? 1 : tokens;
     if (ctas > want) ctas = want;
     s.ctas = ctas;
     s.warps = warps;

@@ -30,6 +30,7 @@ namespace {
 
 constexpr int kBarBytes = 1024;   // mbarriers and hand-off counters at the start of dynamic shared memory
 constexpr int kMaxWarps = 16;
+constexpr unsigned kFlagPatience = 8;   // polls a flag warp holds back a fence for stragglers
 constexpr int kMaxCtas = 160;
 constexpr int kMaxRouteBytes = 64 * 1024;   // largest routing table kept in shared memory
 constexpr int kRedundantEntries = 4096;     // every CTA ranks all tokens up to this many (token, k) pairs
@@ -257,28 +258,29 @@ dispatch_kernel(const RankCtx c, const AttnWs ws, const DispatchArgs a, const Di
         }
     } else if (warp == ND) {
         // Flag warp.  First, in the CTA that holds the source's totals, the count "all-to-all":
-        // per-expert counts and the record count go to every FFN rank ahead of the payload flags.
+        // per-expert counts and the record count go to every FFN rank, each packed with the
+        // epoch into one 8-byte word.  The word is its own arrival flag, so no fence is needed
+        // and the receivers can lay out their rows as soon as the words land.
         if (cta == G - 1 && alive) {
             const int cs = cnt_stride(g);
             for (int idx = lane; idx < F * (EL + 1); idx += 32) {
                 const int f = idx / (EL + 1), el = idx - f * (EL + 1);
                 const int col = (el < EL) ? (F + f * EL + el) : f;
-                int* dst = reinterpret_cast<int*>(c.peer[f] + g.f_cnt) + (size_t)ai * cs + el;
-                *reinterpret_cast<volatile int*>(dst) = lb[col] + tot[col];
+                unsigned long long* dst = reinterpret_cast<unsigned long long*>(c.peer[f] + g.f_cnt) + (size_t)ai * cs + el;
+                ptx::st_relaxed_sys_u64(dst, ((unsigned long long)ep << 32) | (unsigned)(lb[col] + tot[col]));
             }
             __syncwarp();
-            if (lane < F) {
-                ptx::fence_acq_rel_sys();
-                ptx::st_relaxed_sys(reinterpret_cast<uint32_t*>(c.peer[lane] + g.f_cnt_flag) + ai * 32, ep);
-            }
+            if (lane == 0) trace_stamp_here(c.trace, kTraceDispatch, 3);    // counts released
         }
         // Then lane w follows data warp w: one system-scope fence covers every token handed
-        // over since the last one, so the fence never stalls a data warp.
+        // over since the last one, so the fence never stalls a data warp.  A fence costs
+        // microseconds while remote stores are in flight, so the warp waits (briefly) until every
+        // data warp that still owes flags has something new before it pays for one.
         const int mine = (lane < ND) ? tokens_of(lane) : 0;
         int flagged = 0;
         bool aborted = false;
         const long long t_begin = clock64();
-        unsigned idle = 0;
+        unsigned idle = 0, patience = 0;
         while (true) {
             int d = (lane < ND && !aborted) ? ptx::ld_acquire_cta_shared(&done_cnt[lane]) : flagged;
             if (d < 0) {
@@ -286,17 +288,22 @@ dispatch_kernel(const RankCtx c, const AttnWs ws, const DispatchArgs a, const Di
                 d = flagged;
             }
             if (d > flagged && a.flag_mode == 1) flagged = d;      // the data warps already did it
-            if (d > flagged) {
-                ptx::fence_acq_rel_sys();
-                for (int j = flagged; j < d; ++j) {
-                    const int t = token_of(lane, j);
-                    for (int f = 0; f < F; ++f) {
-                        const int s = slot_of(t, f);
-                        if (s >= 0 && s < C)
-                            ptx::st_relaxed_sys(reinterpret_cast<uint32_t*>(c.peer[f] + g.f_slot_flag) + (size_t)ai * C + s, ep);
+            const unsigned fresh = __ballot_sync(ptx::kFullMask, d > flagged);
+            const unsigned owing = __ballot_sync(ptx::kFullMask, lane < ND && !aborted && flagged < mine);
+            if (fresh != 0 && (fresh == owing || ++patience > kFlagPatience)) {
+                patience = 0;
+                if (d > flagged) {
+                    ptx::fence_acq_rel_sys();
+                    for (int j = flagged; j < d; ++j) {
+                        const int t = token_of(lane, j);
+                        for (int f = 0; f < F; ++f) {
+                            const int s = slot_of(t, f);
+                            if (s >= 0 && s < C)
+                                ptx::st_relaxed_sys(reinterpret_cast<uint32_t*>(c.peer[f] + g.f_slot_flag) + (size_t)ai * C + s, ep);
+                        }
                     }
+                    flagged = d;
                 }
-                flagged = d;
                 idle = 0;
             }
             const bool fin = lane >= ND || aborted || flagged >= mine;

@@ -40,33 +40,64 @@ __device__ __forceinline__ int align_up_dev(int v, int a) { return (v + a - 1) /
 
 // Runs in every CTA of the receive kernel (and alone in the layout kernel).  Returns false,
 // uniformly for the CTA, if a source's counts never arrived.
+//
+// A source publishes each count as one 8-byte word (epoch << 32 | count), which is its own
+// arrival flag: a thread fetches a batch of words with independent loads and spins (bounded)
+// only on those that do not carry this exchange's epoch yet.  The raw counts are parked in
+// row_base / rec_prefix and turned into prefix sums in place.
 __device__ bool compute_layout(const RankCtx& c, const WaitCtx& wc, unsigned ep, LayoutSmem& L) {
     const Geometry& g = c.g;
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, nthr = blockDim.x;
     const int A = g.attn, EL = g.experts_local, cs = cnt_stride(g);
     unsigned char* heap = reinterpret_cast<unsigned char*>(c.peer[c.rank]);
-    const uint32_t* cnt_flag = reinterpret_cast<const uint32_t*>(heap + g.f_cnt_flag);
-    const int* cnt = reinterpret_cast<const int*>(heap + g.f_cnt);
+    const unsigned long long* cnt = reinterpret_cast<const unsigned long long*>(heap + g.f_cnt);
     if (tid == 0) L.dead = 0;
     __syncthreads();
-    if (tid < A) {
-        uint32_t seen = 0;
-        const bool ok = spin_until(wc, [&] {
-            seen = ptx::ld_acquire_sys(cnt_flag + tid * 32);
-            return seen == ep;
-        });
-        if (!ok) {
-            report(wc, kTimeoutCounts, g.ffn + tid, ep, ep, seen);
-            poison(wc);
-            L.dead = 1;
+    constexpr int kBatch = 8;
+    const int nwords = A * (EL + 1);
+    for (int base = tid; base < nwords; base += kBatch * nthr) {
+        unsigned long long v[kBatch];
+#pragma unroll
+        for (int q = 0; q < kBatch; ++q) {
+            const int idx = base + q * nthr;
+            if (idx < nwords) {
+                const int a = idx / (EL + 1), el = idx - a * (EL + 1);
+                v[q] = ptx::ld_relaxed_sys_u64(cnt + (size_t)a * cs + el);
+            }
+        }
+#pragma unroll
+        for (int q = 0; q < kBatch; ++q) {
+            const int idx = base + q * nthr;
+            if (idx >= nwords) continue;
+            const int a = idx / (EL + 1), el = idx - a * (EL + 1);
+            unsigned long long w = v[q];
+            if ((unsigned)(w >> 32) != ep) {
+                const unsigned long long* src = cnt + (size_t)a * cs + el;
+                const bool ok = spin_until(wc, [&] {
+                    w = ptx::ld_relaxed_sys_u64(src);
+                    return (unsigned)(w >> 32) == ep;
+                });
+                if (!ok) {
+                    report(wc, kTimeoutCounts, g.ffn + a, ep, ep, (long long)(w >> 32), el);
+                    poison(wc);
+                    L.dead = 1;
+                    w = 0;
+                }
+            }
+            const int n = (int)(unsigned)(w & 0xffffffffull);
+            if (el < EL)
+                L.row_base[a * EL + el] = n;
+            else
+                L.rec_prefix[a + 1] = n;
         }
     }
     __syncthreads();
     if (L.dead) return false;
+    trace_stamp(c.trace, kTraceReceive, 3);     // counts of every source have arrived
 
-    for (int el = tid; el < EL; el += blockDim.x) {
+    for (int el = tid; el < EL; el += nthr) {
         int t = 0;
-        for (int a = 0; a < A; ++a) t += __ldcg(cnt + a * cs + el);
+        for (int a = 0; a < A; ++a) t += L.row_base[a * EL + el];
         L.tot[el] = t;
     }
     __syncthreads();
@@ -87,20 +118,22 @@ __device__ bool compute_layout(const RankCtx& c, const WaitCtx& wc, unsigned ep,
             run += align_up_dev(L.tot[el], g.alignment);
         }
     }
-    if (tid == 32 || (blockDim.x <= 32 && tid == 0)) {
-        int run = 0;
+    if (tid == 32 || (nthr <= 32 && tid == 0)) {
+        int run = 0;      // rec_prefix[a + 1] holds source a's record count; make it a prefix sum in place
         for (int a = 0; a < A; ++a) {
+            const int n = L.rec_prefix[a + 1];
             L.rec_prefix[a] = run;
-            run += __ldcg(cnt + a * cs + EL);
+            run += n;
         }
         L.rec_prefix[A] = run;
     }
     __syncthreads();
-    for (int el = tid; el < EL; el += blockDim.x) {
+    for (int el = tid; el < EL; el += nthr) {
         int run = L.start[el];
         for (int a = 0; a < A; ++a) {
+            const int n = L.row_base[a * EL + el];
             L.row_base[a * EL + el] = run;
-            run += __ldcg(cnt + a * cs + el);
+            run += n;
         }
     }
     __syncthreads();
@@ -226,7 +259,10 @@ receive_kernel(const RankCtx c, const FfnWs ws, const ReceiveArgs r) {
     const int total = ok ? L.rec_prefix[A] : 0;
     const int sg = g.fp8 ? g.scale_groups : 0;
     unsigned char* rx = static_cast<unsigned char*>(r.recv_x);
-    const int first = cta * NW + warp, stride = G * NW;
+    // Work item j of the striped order goes to CTA j % G first and to the next warp only after
+    // every CTA has one: a decode-sized exchange then uses every SM's copy engine for one
+    // record instead of filling a few SMs with kMaxWarps records each.
+    const int first = warp * G + cta, stride = G * NW;
     const int n_w = first < total ? (total - first + stride - 1) / stride : 0;
 
     auto locate = [&](int i, int& a, int& slot) { locate_striped(L, A, first + i * stride, a, slot); };
@@ -255,6 +291,7 @@ receive_kernel(const RankCtx c, const FfnWs ws, const ReceiveArgs r) {
                 }
             }
             if (state == 1) {
+                if (i == 0) trace_stamp(c.trace, kTraceReceiveFirst, 0);
                 uint64_t* bar = &bars[warp * NB + (i % NB)];
                 ptx::fence_proxy_async_global();
                 ptx::mbar_expect_tx(bar, used);
@@ -283,6 +320,7 @@ receive_kernel(const RankCtx c, const FfnWs ws, const ReceiveArgs r) {
         bool landed = spin_until(wc, [&] { return ptx::mbar_try_wait(bar, parity); });
         landed = __all_sync(ptx::kFullMask, landed);
         if (!landed) break;
+        if (i == 0) trace_stamp(c.trace, kTraceReceiveFirst, 1);
         int a, slot;
         locate(i, a, slot);
 
@@ -311,6 +349,7 @@ receive_kernel(const RankCtx c, const FfnWs ws, const ReceiveArgs r) {
             for (int gi = lane; gi < sg; gi += 32) r.recv_scale[(size_t)rk * r.rs0 + (size_t)gi * r.rs1] = sc[gi];
         }
         if (lane == 0) ptx::bulk_commit();
+        if (i == 0) trace_stamp(c.trace, kTraceReceiveFirst, 2);
         if (row >= 0) {
             r.recv_w[row] = w;
             r.recv_src[2 * (size_t)row] = a;
@@ -319,6 +358,7 @@ receive_kernel(const RankCtx c, const FfnWs ws, const ReceiveArgs r) {
         __syncwarp();
     }
     if (lane == 0) ptx::bulk_wait<0>();
+    if (n_w > 0) trace_stamp(c.trace, kTraceReceiveFirst, 3);
 
     __syncthreads();
     trace_stamp(c.trace, kTraceReceive, 2);
@@ -352,6 +392,7 @@ __device__ __forceinline__ uint4 pack_bf16x8(const float* acc) {
     return v;
 }
 
+constexpr unsigned kReplyFlagPatience = 8;   // polls the flag warp holds back a fence for stragglers
 constexpr int kReplyWarps = 8;   // seven reducing warps (16 loads per lane in flight) and one flag warp
 
 __global__ void __launch_bounds__(kReplyWarps * 32, 2)
@@ -475,20 +516,27 @@ reply_kernel(const RankCtx c, const FfnWs ws, const unsigned char* __restrict__ 
         // every warp has handed it over, lanes share the flags; otherwise lane w follows warp w.
         const int mine = coop ? count_from(cta) : ((lane < ND) ? count_from(cta * ND + lane) : 0);
         int flagged = 0;
-        unsigned idle = 0;
+        unsigned idle = 0, patience = 0;
         const long long t_begin = clock64();
         while (true) {
             int d = (lane < ND) ? ptx::ld_acquire_cta_shared(&s_done[lane]) : (coop ? mine : 0);
             if (coop) d = __reduce_min_sync(ptx::kFullMask, d);
-            if (d > flagged) {
-                ptx::fence_acq_rel_sys();
-                for (int j = coop ? flagged + lane : flagged; j < d; j += coop ? 32 : 1) {
-                    int a, slot;
-                    locate((coop ? cta : cta * ND + lane) + j * stride, a, slot);
-                    uint32_t* flag = reinterpret_cast<uint32_t*>(c.peer[g.ffn + a] + g.a_reply_flag) + (size_t)fi * C + slot;
-                    ptx::st_relaxed_sys(flag, ep);
+            // A fence costs microseconds while stores are in flight: hold it back (briefly) until
+            // every reducing warp that still owes flags has handed something over.
+            const unsigned fresh = __ballot_sync(ptx::kFullMask, d > flagged);
+            const unsigned owing = __ballot_sync(ptx::kFullMask, flagged < mine);
+            if (fresh != 0 && (fresh == owing || ++patience > kReplyFlagPatience)) {
+                patience = 0;
+                if (d > flagged) {
+                    ptx::fence_acq_rel_sys();
+                    for (int j = coop ? flagged + lane : flagged; j < d; j += coop ? 32 : 1) {
+                        int a, slot;
+                        locate((coop ? cta : cta * ND + lane) + j * stride, a, slot);
+                        uint32_t* flag = reinterpret_cast<uint32_t*>(c.peer[g.ffn + a] + g.a_reply_flag) + (size_t)fi * C + slot;
+                        ptx::st_relaxed_sys(flag, ep);
+                    }
+                    flagged = d;
                 }
-                flagged = d;
                 idle = 0;
             }
             if (__all_sync(ptx::kFullMask, flagged >= mine)) break;

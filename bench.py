@@ -499,6 +499,23 @@ def main() -> None:
                     f"rank {r} {names[k]:9s} ctas={int(used.sum()):3d} start_ns={s0 % 10**9:9d} phase1_end={p1:7.1f}us "
                     f"first_cta_end={(int(t[:, 2].min()) - s0) / 1e3:7.1f}us last_cta_end={(int(t[:, 2].max()) - s0) / 1e3:7.1f}us"
                 )
+                if k in (0, 1) and (t[:, 3] >= s0).any():
+                    col = t[:, 3][t[:, 3] >= s0]
+                    what = "counts released" if k == 0 else "counts arrived"
+                    lines.append(f"rank {r} {names[k]:9s} {what} at {(int(col.min()) - s0) / 1e3:.1f}..{(int(col.max()) - s0) / 1e3:.1f}us")
+                # progress of warp 0's first record (receive) / token (collect) per CTA, min..max over CTAs
+                detail = {1: (5, ("flag_seen", "landed", "stores_committed", "stores_complete")), 3: (6, ("flags_seen", "rows_landed", "stored"))}
+                if k in detail and tr.shape[0] > detail[k][0]:
+                    d = tr[detail[k][0]]
+                    live = d[:, 0] >= s0
+                    if live.any():
+                        parts = []
+                        for j, label in enumerate(detail[k][1]):
+                            col = d[live][:, j]
+                            col = col[col >= s0]
+                            if col.numel():
+                                parts.append(f"{label}={(int(col.min()) - s0) / 1e3:.1f}..{(int(col.max()) - s0) / 1e3:.1f}us")
+                        lines.append(f"rank {r} {names[k]:9s} first item per CTA ({int(live.sum())} CTAs): " + " ".join(parts))
         if multi:
             alll = [None] * n
             dist.all_gather_object(alll, lines)
