@@ -22,6 +22,12 @@ struct GroupedGemmArgs {
     const float* a_scale;     // element (row, kb) at a_scale[row * s0 + kb * s1]
     long long a_scale_s0, a_scale_s1;
     const float* w_scale;     // [experts][N / 128][K / 128]
+    // Optional, FP8 operands with swiglu only: write the SwiGLU output as e4m3 with one fp32
+    // scale per row and 128 columns (amax / 448) instead of BF16 `out`, ready to be the A operand
+    // of an FP8 down projection.  Needs N to be a multiple of 256.
+    unsigned char* out_q;     // [rows, ldc] e4m3
+    float* out_q_scale;       // element (row, g) at out_q_scale[row * oqs0 + g * oqs1], g < ldc / 128
+    long long oqs0, oqs1;
     int* error;          // optional device word set to 1 if a bounded wait gave up
 };
 

@@ -54,6 +54,9 @@ struct Ctrl {
     int failed;
     int tile_prefix[kMaxExpertsLocal + 1];    // tiles of experts [0, e), in units of (m tiles * n tiles)
     int seg_start[kMaxExpertsLocal];
+    // FP8 output: (tile number << 32 | row amax bits) per [tile parity][column half][tile row], so
+    // the two warps that hold the halves of a 128-column scale group can agree on its scale
+    unsigned long long amax_x[2][2][BM];
 };
 
 // Bounded mbarrier wait: gives up (and makes every role leave) instead of hanging.
@@ -212,7 +215,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int r_in_tile = quarter * 32 + lane;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
         int acc_use = 0;
-        for (int w = blockIdx.x; w < total_work && !*failed; w += gridDim.x) {
+        unsigned tile_no = 0;                    // tiles this CTA has finished, the same in every warp
+        for (int w = blockIdx.x; w < total_work && !*failed; w += gridDim.x, ++tile_no) {
             int e, row0, col0;
             decode(w, e, row0, col0);
             const int hcol0 = col0 + half * HN;                 // first column of this warp's half
@@ -283,7 +287,63 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const float rs = (p.row_scale != nullptr && row_ok) ? p.row_scale[row] : 1.f;
             __nv_bfloat16* out_row = p.out + (size_t)(row_ok ? row : 0) * p.ldc;
             const uint32_t tbase = tmem + lane_base + (uint32_t)(buf * BN + half * HN);
-            if (p.swiglu) {
+            if (kFp8 && p.swiglu && p.out_q != nullptr) {
+                // SwiGLU output quantised to e4m3 in the epilogue.  This thread holds 64 of the 128
+                // output columns of its row's scale group (the tile's 256 gate|up columns); the
+                // warp with the other column half of the same rows holds the rest.  The two trade
+                // their row maxima through shared memory, tagged with the tile number, in a slot
+                // pair that alternates from tile to tile (a warp cannot run two tiles ahead of its
+                // partner, because it needs the partner's value for the tile in between).
+                float m = 0.f;
+#pragma unroll
+                for (int sub = 0; sub < HN / 64; ++sub) {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        const int ig = kFp8 ? sub * 64 + c : 0, iu = kFp8 ? sub * 64 + 32 + c : 0;
+                        const float hval = silu(acc[ig]) * acc[iu] * rs;
+                        acc[ig] = hval;          // the gate slot now holds the output value
+                        m = fmaxf(m, fabsf(hval));
+                    }
+                }
+                const unsigned seq = tile_no + 1u;
+                volatile unsigned long long* slot_mine = &ctrl->amax_x[tile_no & 1u][half][r_in_tile];
+                volatile unsigned long long* slot_other = &ctrl->amax_x[tile_no & 1u][half ^ 1][r_in_tile];
+                *slot_mine = ((unsigned long long)seq << 32) | __float_as_uint(m);
+                unsigned long long other = 0;
+                bool got = false;
+                for (unsigned i = 0; i < kSpinLimit; ++i) {
+                    other = *slot_other;
+                    if ((unsigned)(other >> 32) == seq) {
+                        got = true;
+                        break;
+                    }
+                    if ((i & 1023u) == 1023u && *failed) break;
+                }
+                if (!got) {
+                    *failed = 1;
+                    break;
+                }
+                m = fmaxf(fmaxf(m, __uint_as_float((unsigned)(other & 0xffffffffull))), 1e-12f);
+                const float inv = 448.f / m;
+                if (row_ok) {
+                    unsigned char* dst = p.out_q + (size_t)row * p.ldc + hcol0 / 2;
+#pragma unroll
+                    for (int sub = 0; sub < HN / 64; ++sub) {
+#pragma unroll
+                        for (int c = 0; c < 32; c += 16) {
+                            uint4 pk;
+                            unsigned short* q = reinterpret_cast<unsigned short*>(&pk);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const int i0 = kFp8 ? sub * 64 + c + 2 * i : 0;
+                                q[i] = __nv_cvt_float2_to_fp8x2(make_float2(acc[i0] * inv, acc[kFp8 ? i0 + 1 : 0] * inv), __NV_SATFINITE, __NV_E4M3);
+                            }
+                            *reinterpret_cast<uint4*>(dst + sub * 32 + c) = pk;
+                        }
+                    }
+                    if (half == 0) p.out_q_scale[(size_t)row * p.oqs0 + (size_t)(col0 / BN) * p.oqs1] = m / 448.f;
+                }
+            } else if (p.swiglu) {
                 // every 64 columns hold 32 gate columns followed by their 32 up columns
 #pragma unroll
                 for (int sub = 0; sub < HN / 64; ++sub) {

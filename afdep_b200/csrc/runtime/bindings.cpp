@@ -541,10 +541,12 @@ CUtensorMap make_tile_map(const void* base, int64_t rows, int64_t cols, int elem
 
 // out[rows, N or N/2] = A[rows, K] x W[e][N, K]^T per expert segment, on tcgen05.
 // a: bf16 or e4m3 [rows, K]; w: same dtype [experts, N, K]; ends: int32 [experts].
-torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& w, const torch::Tensor& ends, int64_t alignment,
-                           bool swiglu, const c10::optional<torch::Tensor>& row_scale,
-                           const c10::optional<torch::Tensor>& a_scale, const c10::optional<torch::Tensor>& w_scale,
-                           const c10::optional<torch::Tensor>& out_opt, int64_t ctas) {
+// Returns the BF16 output, or with quantize_out (FP8 operands + swiglu) the pair
+// (e4m3 output [rows, N/2], fp32 scales [rows, N/256]).
+py::object grouped_gemm(const torch::Tensor& a, const torch::Tensor& w, const torch::Tensor& ends, int64_t alignment,
+                        bool swiglu, const c10::optional<torch::Tensor>& row_scale,
+                        const c10::optional<torch::Tensor>& a_scale, const c10::optional<torch::Tensor>& w_scale,
+                        const c10::optional<torch::Tensor>& out_opt, int64_t ctas, bool quantize_out) {
     TORCH_CHECK(a.is_cuda() && w.is_cuda() && ends.is_cuda(), "grouped_gemm needs CUDA tensors");
     TORCH_CHECK(a.dim() == 2 && w.dim() == 3 && a.is_contiguous() && w.is_contiguous(), "a [rows,K], w [experts,N,K], contiguous");
     TORCH_CHECK(a.scalar_type() == w.scalar_type(), "a and w must have the same dtype");
@@ -558,11 +560,19 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& w, const
                 "operands must be 16-byte aligned");
     c10::cuda::CUDAGuard guard(a.device());
     const int64_t ldc = swiglu ? N / 2 : N;
-    torch::Tensor out = out_opt.has_value()
-                            ? *out_opt
-                            : torch::empty({rows, ldc}, torch::TensorOptions().dtype(torch::kBFloat16).device(a.device()));
-    TORCH_CHECK(out.scalar_type() == torch::kBFloat16 && out.is_contiguous() && out.size(0) == rows && out.size(1) == ldc,
-                "out must be contiguous bf16 [rows, N or N/2]");
+    torch::Tensor out, out_q, out_q_scale;
+    if (quantize_out) {
+        TORCH_CHECK(fp8 && swiglu && N % 256 == 0 && !out_opt.has_value(),
+                    "quantize_out needs FP8 operands, swiglu, N a multiple of 256 and no preallocated out");
+        out_q = torch::empty({rows, ldc}, torch::TensorOptions().dtype(torch::kFloat8_e4m3fn).device(a.device()));
+        out_q_scale = torch::empty({rows, ldc / 128}, torch::TensorOptions().dtype(torch::kFloat32).device(a.device()));
+    } else {
+        out = out_opt.has_value() ? *out_opt
+                                  : torch::empty({rows, ldc}, torch::TensorOptions().dtype(torch::kBFloat16).device(a.device()));
+        TORCH_CHECK(out.scalar_type() == torch::kBFloat16 && out.is_contiguous() && out.size(0) == rows && out.size(1) == ldc,
+                    "out must be contiguous bf16 [rows, N or N/2]");
+    }
+    const py::object result = quantize_out ? py::object(py::make_tuple(out_q, out_q_scale)) : py::cast(out);
     GroupedGemmArgs g{};
     g.rows = (int)rows;
     g.N = (int)N;
@@ -570,7 +580,13 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& w, const
     g.experts = (int)E;
     g.alignment = (int)alignment;
     g.ends = ends.data_ptr<int>();
-    g.out = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
+    g.out = quantize_out ? nullptr : reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
+    if (quantize_out) {
+        g.out_q = static_cast<unsigned char*>(out_q.data_ptr());
+        g.out_q_scale = out_q_scale.data_ptr<float>();
+        g.oqs0 = out_q_scale.stride(0);
+        g.oqs1 = out_q_scale.stride(1);
+    }
     g.ldc = (int)ldc;
     g.swiglu = swiglu ? 1 : 0;
     g.row_scale = row_scale.has_value() ? row_scale->data_ptr<float>() : nullptr;
@@ -585,7 +601,7 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& w, const
         g.a_scale_s1 = a_scale->stride(1);
         g.w_scale = w_scale->data_ptr<float>();
     }
-    if (rows == 0) return out;
+    if (rows == 0) return result;
     const int elem = fp8 ? 1 : 2;
     const CUtensorMap map_a = make_tile_map(a.data_ptr(), rows, K, elem, 128);
     const CUtensorMap map_w = make_tile_map(w.data_ptr(), E * N, K, elem, 256);
@@ -593,7 +609,7 @@ torch::Tensor grouped_gemm(const torch::Tensor& a, const torch::Tensor& w, const
     rt_check(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, a.get_device()), "device attribute");
     const int grid = ctas > 0 ? (int)ctas : sms;
     rt_check(launch_grouped_gemm(map_a, map_w, g, grid, at::cuda::getCurrentCUDAStream().stream()), "grouped_gemm launch");
-    return out;
+    return result;
 }
 
 // (e4m3 [rows, K], fp32 scales [rows, K/128]) from bf16 rows; `limit` (optional int32 device
@@ -644,7 +660,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     });
     m.def("grouped_gemm", &afdep::grouped_gemm, py::arg("a"), py::arg("w"), py::arg("ends"), py::arg("alignment"),
           py::arg("swiglu") = false, py::arg("row_scale") = py::none(), py::arg("a_scale") = py::none(),
-          py::arg("w_scale") = py::none(), py::arg("out") = py::none(), py::arg("ctas") = 0);
+          py::arg("w_scale") = py::none(), py::arg("out") = py::none(), py::arg("ctas") = 0, py::arg("quantize_out") = false);
     m.def("quantize_rows_fp8", &afdep::quantize_rows_fp8, py::arg("x"), py::arg("limit") = py::none());
     m.def("route_layout", &afdep::route_layout, py::arg("ids"), py::arg("num_experts"), py::arg("ffn_ranks"));
     py::class_<NativeBuffer>(m, "NativeBuffer")

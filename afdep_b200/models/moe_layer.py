@@ -10,9 +10,11 @@ The expert path is two grouped GEMMs (`afdep_b200.ops.grouped_gemm`):
   1. gate|up projection with SwiGLU in the epilogue.  With ``weights="fp8"`` the weights are
      stored e4m3 with one fp32 scale per 128 x 128 block and multiplied with e4m3 activations
      carrying per-row, per-128-column scales (block-scaled FP8, promotion in the epilogue);
-  2. down projection in BF16 with the routing weight applied to every output row.
-The down projection keeps its e4m3-rounded weights in BF16: its input is the BF16 SwiGLU
-output, and the tensor cores do not mix BF16 and FP8 operands.
+  2. down projection with the routing weight applied to every output row.  With FP8 weights
+     the first GEMM's epilogue quantises the SwiGLU output to e4m3 (one scale per row and 128
+     columns), so the down projection is block-scaled FP8 as well and reads half the weight
+     bytes; ``down="bf16"`` keeps the e4m3-rounded down weights in BF16 and the SwiGLU output
+     in BF16 instead (the tensor cores do not mix BF16 and FP8 operands).
 
 The reference library stops at the exchange (its README leaves routing, quantization and
 expert GEMMs to the caller); this module is the "caller" used by the end-to-end benchmark.
@@ -35,14 +37,19 @@ class ExpertWeights:
 
     w_gate_up: torch.Tensor            # [E, 2I, H] bf16 or e4m3, gate/up interleaved in 32-row blocks
     w_gate_up_scale: torch.Tensor | None   # [E, 2I/128, H/128] fp32 (FP8 only)
-    w_down: torch.Tensor               # [E, H, I] bf16
+    w_down: torch.Tensor               # [E, H, I] bf16, or e4m3 when w_down_scale is set
     intermediate: int
     mode: str
+    w_down_scale: torch.Tensor | None = None   # [E, H/128, I/128] fp32 (FP8 down projection only)
 
     @staticmethod
-    def random(num_local_experts: int, hidden: int, intermediate: int, *, mode: str = "bf16", seed: int = 0, device="cuda", std: float = 0.02) -> "ExpertWeights":
-        """Random-init N(0, std) experts; ``mode`` is "bf16" or "fp8" (e4m3 storage, 128 x 128 scales)."""
+    def random(num_local_experts: int, hidden: int, intermediate: int, *, mode: str = "bf16", seed: int = 0, device="cuda", std: float = 0.02,
+               down: str | None = None) -> "ExpertWeights":
+        """Random-init N(0, std) experts; ``mode`` is "bf16" or "fp8" (e4m3 storage, 128 x 128 scales).
+        ``down`` ("fp8" | "bf16", default: like ``mode``) picks the storage of the down projection."""
         assert mode in ("bf16", "fp8")
+        down = down or mode
+        assert down in ("bf16", "fp8") and (down == "bf16" or mode == "fp8"), "an FP8 down projection needs FP8 gate/up weights"
         gen = torch.Generator(device=device).manual_seed(seed)
         E, I, H = num_local_experts, intermediate, hidden
         gate_up = torch.empty((E, 2 * I, H), device=device, dtype=torch.bfloat16)
@@ -56,12 +63,19 @@ class ExpertWeights:
             return ExpertWeights(gate_up, None, down, I, mode)
         q = torch.empty((E, 2 * I, H), device=device, dtype=torch.float8_e4m3fn)
         scale = torch.empty((E, 2 * I // 128, H // 128), device=device, dtype=torch.float32)
+        down_q = torch.empty((E, H, I), device=device, dtype=torch.float8_e4m3fn) if down == "fp8" else None
+        down_scale = torch.empty((E, H // 128, I // 128), device=device, dtype=torch.float32) if down == "fp8" else None
         for e in range(E):
             qe, se = gg.quantize_weight_blocks_fp8(gate_up[e : e + 1].float())
             q[e], scale[e] = qe[0], se[0]
             de, ds = gg.quantize_weight_blocks_fp8(down[e : e + 1].float())
-            blocks = de.float().view(1, H // 128, 128, I // 128, 128) * ds.view(1, H // 128, 1, I // 128, 1)
-            down[e] = blocks.reshape(H, I).to(torch.bfloat16)      # e4m3-rounded values, BF16 storage
+            if down == "fp8":
+                down_q[e], down_scale[e] = de[0], ds[0]
+            else:
+                blocks = de.float().view(1, H // 128, 128, I // 128, 128) * ds.view(1, H // 128, 1, I // 128, 1)
+                down[e] = blocks.reshape(H, I).to(torch.bfloat16)      # e4m3-rounded values, BF16 storage
+        if down == "fp8":
+            return ExpertWeights(q, scale, down_q, I, mode, down_scale)
         return ExpertWeights(q, scale, down, I, mode)
 
 
@@ -74,6 +88,11 @@ def run_experts(received: ReceiveResult, weights: ExpertWeights, alignment: int,
         x, a_scale = gg.quantize_rows_fp8_cuda(x, ends[-1:])
     else:
         a_scale = received.recv_scale
+    if weights.w_down_scale is not None:
+        h_q, h_scale = gg.grouped_gemm(x, weights.w_gate_up, ends, alignment, swiglu=True, a_scale=a_scale,
+                                       w_scale=weights.w_gate_up_scale, quantize_out=True)
+        return gg.grouped_gemm(h_q, weights.w_down, ends, alignment, row_scale=received.recv_topk_weights,
+                               a_scale=h_scale, w_scale=weights.w_down_scale)
     h = gg.grouped_gemm(x, weights.w_gate_up, ends, alignment, swiglu=True, a_scale=a_scale if fp8 else None,
                         w_scale=weights.w_gate_up_scale)
     return gg.grouped_gemm(h, weights.w_down, ends, alignment, row_scale=received.recv_topk_weights)
@@ -88,6 +107,11 @@ def reference_experts(received: ReceiveResult, weights: ExpertWeights, alignment
         x, a_scale = gg.quantize_rows_fp8(x)
     h = gg.reference_grouped_gemm(x, weights.w_gate_up, ends.cpu(), alignment, swiglu=True, a_scale=a_scale if fp8 else None,
                                   w_scale=weights.w_gate_up_scale)
+    if weights.w_down_scale is not None:
+        h_q, h_scale = gg.quantize_rows_fp8(h)
+        y = gg.reference_grouped_gemm(h_q, weights.w_down, ends.cpu(), alignment, row_scale=received.recv_topk_weights,
+                                      a_scale=h_scale, w_scale=weights.w_down_scale)
+        return y.to(torch.bfloat16)
     h = h.to(torch.bfloat16)
     y = gg.reference_grouped_gemm(h, weights.w_down, ends.cpu(), alignment, row_scale=received.recv_topk_weights)
     return y.to(torch.bfloat16)

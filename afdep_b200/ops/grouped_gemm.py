@@ -9,7 +9,8 @@ Operands are BF16, or e4m3 with fp32 block scales (``a_scale [rows, K/128]`` per
 columns, ``w_scale [experts, N/128, K/128]`` per 128 x 128 block).  ``swiglu=True`` expects the
 gate and up projections interleaved in blocks of 32 rows of ``w`` (see ``interleave_gate_up``)
 and returns ``silu(gate) * up`` with ``N/2`` columns; ``row_scale`` multiplies every output
-row (the routing weight).  Rows outside the expert segments are left untouched.
+row (the routing weight); ``quantize_out`` makes the FP8 SwiGLU GEMM emit e4m3 rows with scales,
+so a down projection can run in FP8 too.  Rows outside the expert segments are left untouched.
 """
 
 from __future__ import annotations
@@ -19,10 +20,14 @@ import torch
 GATE_UP_BLOCK = 32   # rows of gate, then rows of up, alternating in the fused gate|up matrix
 
 
-def grouped_gemm(a, w, ends, alignment: int, *, swiglu: bool = False, row_scale=None, a_scale=None, w_scale=None, out=None, ctas: int = 0):
+def grouped_gemm(a, w, ends, alignment: int, *, swiglu: bool = False, row_scale=None, a_scale=None, w_scale=None, out=None, ctas: int = 0,
+                 quantize_out: bool = False):
+    """``quantize_out=True`` (FP8 operands with ``swiglu``): the epilogue quantises the SwiGLU
+    output and returns ``(e4m3 [rows, N/2], fp32 scales [rows, N/256])`` instead of BF16, in the
+    per-row, per-128-column format the FP8 GEMM takes as its ``a`` operand."""
     from .._native import load_native
 
-    return load_native().grouped_gemm(a, w, ends, int(alignment), bool(swiglu), row_scale, a_scale, w_scale, out, int(ctas))
+    return load_native().grouped_gemm(a, w, ends, int(alignment), bool(swiglu), row_scale, a_scale, w_scale, out, int(ctas), bool(quantize_out))
 
 
 def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:

@@ -50,6 +50,7 @@ def parse_args():
     p.add_argument("--impl", choices=("ours", "nccl", "reference"), default="ours")
     p.add_argument("--config", choices=tuple(CONFIGS), default="weak")
     p.add_argument("--expert-weights", choices=("fp8", "bf16"), default="fp8", help="config 5: storage of the expert weights")
+    p.add_argument("--expert-down", choices=("fp8", "bf16"), default=None, help="config 5: storage of the down projection (default: like --expert-weights)")
     p.add_argument("--tokens", type=int, default=0, help="override tokens per attention rank")
     p.add_argument("--num-sms", type=int, default=0)
     p.add_argument("--graph", action="store_true", help="(default for --impl ours) replay each timed step from a CUDA graph")
@@ -230,7 +231,7 @@ def main() -> None:
             from afdep_b200.models.moe_layer import ExpertWeights
 
             s["weights"] = ExpertWeights.random(
-                cfg.experts_per_rank, cfg.hidden_size, spec["intermediate"], mode=args.expert_weights, seed=7 + buf.role_rank, device=dev
+                cfg.experts_per_rank, cfg.hidden_size, spec["intermediate"], mode=args.expert_weights, down=args.expert_down, seed=7 + buf.role_rank, device=dev
             )
         else:
             s["rows"] = torch.zeros((cfg.receive_rows(T), cfg.hidden_size), dtype=torch.bfloat16, device=dev)
@@ -458,6 +459,9 @@ def main() -> None:
             round(6.0 * T * attn * cfg.top_k * cfg.hidden_size * spec["intermediate"] / (ms_per_step * 1e-3) / 1e12, 2)
             if "intermediate" in spec
             else None
+        ),
+        "expert_weights": (
+            {"gate_up": args.expert_weights, "down": args.expert_down or args.expert_weights} if "intermediate" in spec else None
         ),
         "phases": phases,
         "roofline": dict(

@@ -81,6 +81,46 @@ def test_fp8_block_scaled_grouped_gemm(swiglu):
         torch.testing.assert_close(out[s:t].float(), ref[s:t], rtol=2e-2, atol=2e-2)
 
 
+def test_fp8_swiglu_with_quantised_output_feeds_an_fp8_down_projection():
+    """The SwiGLU epilogue can emit e4m3 rows with per-row, per-128-column scales; they must
+    dequantise to the fp32 SwiGLU output within e4m3 rounding, and a second FP8 GEMM on them
+    must match the reference evaluated on the same quantised rows."""
+    torch.manual_seed(4)
+    counts, I, K, H2 = [140, 0, 128, 260], 512, 1024, 384
+    ends, rows = _segments(counts, 128)
+    x = torch.randn(rows, K, device="cuda")
+    a, a_scale = gg.quantize_rows_fp8(x)
+    wg = torch.randn(len(counts), I, K, device="cuda") * 0.03
+    wu = torch.randn(len(counts), I, K, device="cuda") * 0.03
+    w, w_scale = gg.quantize_weight_blocks_fp8(gg.interleave_gate_up(wg, wu))
+    h_q, h_scale = gg.grouped_gemm(a, w, ends.cuda(), 128, swiglu=True, a_scale=a_scale, w_scale=w_scale, quantize_out=True)
+    torch.cuda.synchronize()
+    assert h_q.dtype == torch.float8_e4m3fn and h_q.shape == (rows, I) and h_scale.shape == (rows, I // 128)
+    ref = gg.reference_grouped_gemm(a, w, ends, 128, swiglu=True, a_scale=a_scale, w_scale=w_scale)
+    starts = gg.segment_starts(ends, 128).tolist()
+    for s0, t0 in zip(starts, ends.tolist()):
+        if t0 <= s0:
+            continue
+        r = ref[s0:t0].view(t0 - s0, I // 128, 128)
+        sc = h_scale[s0:t0]
+        torch.testing.assert_close(sc, r.abs().amax(dim=2).clamp_min(1e-12) / 448.0, rtol=2e-2, atol=1e-9)
+        dq = h_q[s0:t0].float().view(t0 - s0, I // 128, 128) * sc[:, :, None]
+        bound = r.abs() * 0.09 + sc[:, :, None] * 2.0 ** -8
+        assert ((dq - r).abs() <= bound).all()
+    # down projection in FP8 on the quantised rows
+    wd, wd_scale = gg.quantize_weight_blocks_fp8(torch.randn(len(counts), H2, I, device="cuda") * 0.03)
+    rs = torch.rand(rows, device="cuda") + 0.5
+    out = gg.grouped_gemm(h_q, wd, ends.cuda(), 128, row_scale=rs, a_scale=h_scale, w_scale=wd_scale)
+    torch.cuda.synchronize()
+    # rows outside the segments hold unspecified bytes: zero them for the reference
+    hq_clean, hs_clean = torch.zeros_like(h_q.float()), torch.ones_like(h_scale)
+    for s0, t0 in zip(starts, ends.tolist()):
+        hq_clean[s0:t0], hs_clean[s0:t0] = h_q[s0:t0].float(), h_scale[s0:t0]
+    ref2 = gg.reference_grouped_gemm(hq_clean.to(torch.float8_e4m3fn), wd, ends, 128, row_scale=rs, a_scale=hs_clean, w_scale=wd_scale)
+    for s0, t0 in zip(starts, ends.tolist()):
+        torch.testing.assert_close(out[s0:t0].float(), ref2[s0:t0], rtol=2e-2, atol=2e-3)
+
+
 def test_fp8_row_quantiser_matches_torch():
     torch.manual_seed(3)
     x = (torch.randn(300, 1024, device="cuda") * 3).bfloat16()

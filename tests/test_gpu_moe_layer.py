@@ -5,13 +5,21 @@ import torch
 
 from afdep_b200 import Config
 from afdep_b200.models.moe_layer import ExpertWeights, reference_experts, run_experts
+from afdep_b200.ops import grouped_gemm as gg
 from afdep_b200.utils import synthetic
 
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("payload,mode", [("bf16", "bf16"), ("fp8", "fp8"), ("bf16", "fp8")])
-def test_moe_layer_matches_dense_reference(payload, mode):
+def _dequant_blocks(w, scale):
+    if scale is None:
+        return w.float()
+    E, N, K = w.shape
+    return (w.float().view(E, N // 128, 128, K // 128, 128) * scale.view(E, N // 128, 1, K // 128, 1)).reshape(E, N, K)
+
+
+@pytest.mark.parametrize("payload,mode,down", [("bf16", "bf16", "bf16"), ("fp8", "fp8", "fp8"), ("bf16", "fp8", "fp8"), ("fp8", "fp8", "bf16")])
+def test_moe_layer_matches_dense_reference(payload, mode, down):
     from afdep_b200.parallel.loopback import LoopbackWorld
 
     hidden, inter, experts, top_k, ffn, attn, tokens = 512, 256, 8, 2, 2, 2, 96
@@ -19,7 +27,7 @@ def test_moe_layer_matches_dense_reference(payload, mode):
     world = LoopbackWorld(cfg, gpu_timeout_s=5.0)
     try:
         el = cfg.experts_per_rank
-        weights = [ExpertWeights.random(el, hidden, inter, mode=mode, seed=10 + f) for f in range(ffn)]
+        weights = [ExpertWeights.random(el, hidden, inter, mode=mode, down=down, seed=10 + f) for f in range(ffn)]
         batches = [synthetic.random_batch(cfg, tokens - 7 * a, seed=a) for a in range(attn)]
         dev = [tuple(None if t is None else t.cuda() for t in b) for b in batches]
         kept = {}
@@ -49,10 +57,8 @@ def test_moe_layer_matches_dense_reference(payload, mode):
             want = torch.zeros_like(xf)
             for f in range(ffn):
                 wt = weights[f]
-                gu = wt.w_gate_up.float()
-                if wt.w_gate_up_scale is not None:
-                    E, N, K = gu.shape
-                    gu = (gu.view(E, N // 128, 128, K // 128, 128) * wt.w_gate_up_scale.view(E, N // 128, 1, K // 128, 1)).reshape(E, N, K)
+                gu = _dequant_blocks(wt.w_gate_up, wt.w_gate_up_scale)
+                wd = _dequant_blocks(wt.w_down, wt.w_down_scale)
                 for le in range(el):
                     e = f * el + le
                     sel = ids == e
@@ -62,7 +68,12 @@ def test_moe_layer_matches_dense_reference(payload, mode):
                     y = xf[tok] @ gu[le].T
                     y = y.view(y.shape[0], -1, 2, 32)
                     h = (torch.nn.functional.silu(y[:, :, 0]) * y[:, :, 1]).reshape(y.shape[0], -1)
-                    o = h.to(torch.bfloat16).float() @ wt.w_down[le].float().T
+                    if wt.w_down_scale is not None:      # the kernels quantise the SwiGLU output for an FP8 down projection
+                        hq, hs = gg.quantize_rows_fp8(h)
+                        h = (hq.float().view(h.shape[0], -1, 128) * hs[:, :, None]).reshape(h.shape)
+                    else:
+                        h = h.to(torch.bfloat16).float()
+                    o = h @ wd[le].T
                     want[tok] += o * (w * sel)[tok].sum(dim=1, keepdim=True)
             torch.testing.assert_close(out.float(), want, rtol=5e-2, atol=5e-3)
     finally:
