@@ -62,12 +62,9 @@ dispatch_kernel(const RankCtx c, const AttnWs ws, const DispatchArgs a, const Di
     const int ai = c.role_rank;
     const unsigned ep = ptx::ld_acquire_gpu(&ws.epoch[0]) + 1u;
     const WaitCtx wc{c.status, c.poison, c.budget, c.rank, /*kernel=*/1};
-    (void)L;
     trace_stamp(c.trace, kTraceDispatch, 0);
 
     const int T = a.T;
-    int t0, t1;
-    route_layout_chunk(T, t0, t1);
 
     // shared memory: [bars | routing table | totals | overlay: layout histograms, then record buffers]
     int* local = plan.route_rows ? reinterpret_cast<int*>(smem + kBarBytes) : nullptr;
