@@ -546,7 +546,7 @@ CUtensorMap make_tile_map(const void* base, int64_t rows, int64_t cols, int elem
 py::object grouped_gemm(const torch::Tensor& a, const torch::Tensor& w, const torch::Tensor& ends, int64_t alignment,
                         bool swiglu, const c10::optional<torch::Tensor>& row_scale,
                         const c10::optional<torch::Tensor>& a_scale, const c10::optional<torch::Tensor>& w_scale,
-                        const c10::optional<torch::Tensor>& out_opt, int64_t ctas, bool quantize_out) {
+                        const c10::optional<torch::Tensor>& out_opt, int64_t ctas, bool quantize_out, bool swapped) {
     TORCH_CHECK(a.is_cuda() && w.is_cuda() && ends.is_cuda(), "grouped_gemm needs CUDA tensors");
     TORCH_CHECK(a.dim() == 2 && w.dim() == 3 && a.is_contiguous() && w.is_contiguous(), "a [rows,K], w [experts,N,K], contiguous");
     TORCH_CHECK(a.scalar_type() == w.scalar_type(), "a and w must have the same dtype");
@@ -562,8 +562,8 @@ py::object grouped_gemm(const torch::Tensor& a, const torch::Tensor& w, const to
     const int64_t ldc = swiglu ? N / 2 : N;
     torch::Tensor out, out_q, out_q_scale;
     if (quantize_out) {
-        TORCH_CHECK(fp8 && swiglu && N % 256 == 0 && !out_opt.has_value(),
-                    "quantize_out needs FP8 operands, swiglu, N a multiple of 256 and no preallocated out");
+        TORCH_CHECK(fp8 && swiglu && N % 256 == 0 && !out_opt.has_value() && !swapped,
+                    "quantize_out needs FP8 operands, swiglu, N a multiple of 256, the wide tile and no preallocated out");
         out_q = torch::empty({rows, ldc}, torch::TensorOptions().dtype(torch::kFloat8_e4m3fn).device(a.device()));
         out_q_scale = torch::empty({rows, ldc / 128}, torch::TensorOptions().dtype(torch::kFloat32).device(a.device()));
     } else {
@@ -603,11 +603,17 @@ py::object grouped_gemm(const torch::Tensor& a, const torch::Tensor& w, const to
     }
     if (rows == 0) return result;
     const int elem = fp8 ? 1 : 2;
-    const CUtensorMap map_a = make_tile_map(a.data_ptr(), rows, K, elem, 128);
-    const CUtensorMap map_w = make_tile_map(w.data_ptr(), E * N, K, elem, 256);
     int sms = 0;
     rt_check(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, a.get_device()), "device attribute");
     const int grid = ctas > 0 ? (int)ctas : sms;
+    if (swapped) {       // small batches: weights are the 128-row operand, tokens the 64-wide one
+        const CUtensorMap map_w = make_tile_map(w.data_ptr(), E * N, K, elem, 128);
+        const CUtensorMap map_a = make_tile_map(a.data_ptr(), rows, K, elem, 64);
+        rt_check(launch_grouped_gemm_swapped(map_w, map_a, g, grid, at::cuda::getCurrentCUDAStream().stream()), "grouped_gemm launch");
+        return result;
+    }
+    const CUtensorMap map_a = make_tile_map(a.data_ptr(), rows, K, elem, 128);
+    const CUtensorMap map_w = make_tile_map(w.data_ptr(), E * N, K, elem, 256);
     rt_check(launch_grouped_gemm(map_a, map_w, g, grid, at::cuda::getCurrentCUDAStream().stream()), "grouped_gemm launch");
     return result;
 }
@@ -660,7 +666,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     });
     m.def("grouped_gemm", &afdep::grouped_gemm, py::arg("a"), py::arg("w"), py::arg("ends"), py::arg("alignment"),
           py::arg("swiglu") = false, py::arg("row_scale") = py::none(), py::arg("a_scale") = py::none(),
-          py::arg("w_scale") = py::none(), py::arg("out") = py::none(), py::arg("ctas") = 0, py::arg("quantize_out") = false);
+          py::arg("w_scale") = py::none(), py::arg("out") = py::none(), py::arg("ctas") = 0, py::arg("quantize_out") = false, py::arg("swapped") = false);
     m.def("quantize_rows_fp8", &afdep::quantize_rows_fp8, py::arg("x"), py::arg("limit") = py::none());
     m.def("route_layout", &afdep::route_layout, py::arg("ids"), py::arg("num_experts"), py::arg("ffn_ranks"));
     py::class_<NativeBuffer>(m, "NativeBuffer")

@@ -79,8 +79,10 @@ class ExpertWeights:
         return ExpertWeights(q, scale, down, I, mode)
 
 
-def run_experts(received: ReceiveResult, weights: ExpertWeights, alignment: int, *, scratch: dict | None = None) -> torch.Tensor:
-    """BF16 rows for ``worker_reply``: SwiGLU MLP of every received row, times its routing weight."""
+def run_experts(received: ReceiveResult, weights: ExpertWeights, alignment: int, *, scratch: dict | None = None,
+                tile: str | None = None) -> torch.Tensor:
+    """BF16 rows for ``worker_reply``: SwiGLU MLP of every received row, times its routing weight.
+    ``tile`` picks the GEMM tile shape ("wide", the default, or "swapped")."""
     x, ends = received.recv_x, received.recv_count_psum
     fp8 = weights.mode == "fp8"
     if fp8 and x.dtype != torch.float8_e4m3fn:
@@ -88,14 +90,21 @@ def run_experts(received: ReceiveResult, weights: ExpertWeights, alignment: int,
         x, a_scale = gg.quantize_rows_fp8_cuda(x, ends[-1:])
     else:
         a_scale = received.recv_scale
+    tile = tile or "wide"
     if weights.w_down_scale is not None:
-        h_q, h_scale = gg.grouped_gemm(x, weights.w_gate_up, ends, alignment, swiglu=True, a_scale=a_scale,
-                                       w_scale=weights.w_gate_up_scale, quantize_out=True)
+        if tile == "swapped":
+            # no quantising epilogue in the swapped kernel: BF16 SwiGLU output, one small quantiser launch
+            h = gg.grouped_gemm(x, weights.w_gate_up, ends, alignment, swiglu=True, a_scale=a_scale,
+                                w_scale=weights.w_gate_up_scale, tile=tile)
+            h_q, h_scale = gg.quantize_rows_fp8_cuda(h, ends[-1:])
+        else:
+            h_q, h_scale = gg.grouped_gemm(x, weights.w_gate_up, ends, alignment, swiglu=True, a_scale=a_scale,
+                                           w_scale=weights.w_gate_up_scale, quantize_out=True)
         return gg.grouped_gemm(h_q, weights.w_down, ends, alignment, row_scale=received.recv_topk_weights,
-                               a_scale=h_scale, w_scale=weights.w_down_scale)
+                               a_scale=h_scale, w_scale=weights.w_down_scale, tile=tile)
     h = gg.grouped_gemm(x, weights.w_gate_up, ends, alignment, swiglu=True, a_scale=a_scale if fp8 else None,
-                        w_scale=weights.w_gate_up_scale)
-    return gg.grouped_gemm(h, weights.w_down, ends, alignment, row_scale=received.recv_topk_weights)
+                        w_scale=weights.w_gate_up_scale, tile=tile)
+    return gg.grouped_gemm(h, weights.w_down, ends, alignment, row_scale=received.recv_topk_weights, tile=tile)
 
 
 def reference_experts(received: ReceiveResult, weights: ExpertWeights, alignment: int) -> torch.Tensor:

@@ -30,6 +30,7 @@ def main() -> None:
     p.add_argument("--iters", type=int, default=10)
     p.add_argument("--ctas", type=int, default=0)
     p.add_argument("--skip-cublas", action="store_true")
+    p.add_argument("--tile", choices=("wide", "swapped"), default="wide", help="128 x 256 tiles, or 128 weight rows x 64 tokens")
     a = p.parse_args()
     torch.cuda.set_device(0)
     E, N, K, R = a.experts, a.n, a.k, a.rows_per_expert
@@ -67,7 +68,7 @@ def main() -> None:
                 ts.append(e0.elapsed_time(e1))
         return sum(ts) / len(ts), min(ts)
 
-    mean_ms, best_ms = timed(lambda: gg.grouped_gemm(xa, wa, ends, 128, swiglu=a.swiglu, out=out, ctas=a.ctas, **kw))
+    mean_ms, best_ms = timed(lambda: gg.grouped_gemm(xa, wa, ends, 128, swiglu=a.swiglu, out=out, ctas=a.ctas, tile=a.tile, **kw))
     peaks = {}
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -75,7 +76,7 @@ def main() -> None:
     bf16_peak = peaks.get("bf16_tflops", 1590.0)
     peak = bf16_peak * (2.0 if a.dtype == "fp8" else 1.0)
     res = {
-        "kernel": "grouped_gemm", "dtype": a.dtype, "swiglu": a.swiglu, "experts": E, "rows_per_expert": R, "N": N, "K": K,
+        "kernel": "grouped_gemm", "tile": a.tile, "dtype": a.dtype, "swiglu": a.swiglu, "experts": E, "rows_per_expert": R, "N": N, "K": K,
         "ms_mean": round(mean_ms, 4), "ms_best": round(best_ms, 4),
         "tflops_mean": round(flops / mean_ms / 1e9, 1), "tflops_best": round(flops / best_ms / 1e9, 1),
         "peak_tflops": peak, "peak_source": "measured cuBLAS bf16" + (" x2 for fp8" if a.dtype == "fp8" else "") if peaks else "fallback",

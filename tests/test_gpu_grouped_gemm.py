@@ -18,14 +18,18 @@ def _segments(counts, alignment):
     return torch.tensor(ends, dtype=torch.int32), rows
 
 
+TILES = ["wide", "swapped"]     # 128 rows x 256 columns per tile, or 128 weight rows x 64 tokens
+
+
+@pytest.mark.parametrize("tile", TILES)
 @pytest.mark.parametrize("counts,N,K", [([128], 128, 64 * 2), ([100, 0, 300, 128], 256, 512), ([37, 260, 129, 5, 640, 1], 512, 1024)])
-def test_bf16_grouped_gemm(counts, N, K):
+def test_bf16_grouped_gemm(counts, N, K, tile):
     torch.manual_seed(0)
     ends, rows = _segments(counts, 128)
     a = (torch.randn(rows, K, device="cuda") * 0.5).bfloat16()
     w = (torch.randn(len(counts), N, K, device="cuda") * 0.05).bfloat16()
     out = torch.full((rows, N), 7.0, device="cuda", dtype=torch.bfloat16)
-    gg.grouped_gemm(a, w, ends.cuda(), 128, out=out)
+    gg.grouped_gemm(a, w, ends.cuda(), 128, out=out, tile=tile)
     torch.cuda.synchronize()
     ref = gg.reference_grouped_gemm(a, w, ends, 128)
     starts = gg.segment_starts(ends, 128).tolist()
@@ -38,7 +42,8 @@ def test_bf16_grouped_gemm(counts, N, K):
     assert (out[mask.cuda()] == 7.0).all()
 
 
-def test_bf16_swiglu_and_row_scale():
+@pytest.mark.parametrize("tile", TILES)
+def test_bf16_swiglu_and_row_scale(tile):
     torch.manual_seed(1)
     counts, I, K = [200, 77, 0, 130], 256, 512
     ends, rows = _segments(counts, 128)
@@ -47,7 +52,7 @@ def test_bf16_swiglu_and_row_scale():
     wu = (torch.randn(len(counts), I, K, device="cuda") * 0.05).bfloat16()
     w = gg.interleave_gate_up(wg, wu)
     scale = torch.rand(rows, device="cuda") + 0.5
-    out = gg.grouped_gemm(a, w, ends.cuda(), 128, swiglu=True, row_scale=scale)
+    out = gg.grouped_gemm(a, w, ends.cuda(), 128, swiglu=True, row_scale=scale, tile=tile)
     torch.cuda.synchronize()
     ref = gg.reference_grouped_gemm(a, w, ends, 128, swiglu=True, row_scale=scale)
     # direct statement of the same thing from the un-interleaved matrices
@@ -61,8 +66,9 @@ def test_bf16_swiglu_and_row_scale():
         torch.testing.assert_close(out[s:t].float(), ref[s:t], rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("tile", TILES)
 @pytest.mark.parametrize("swiglu", [False, True])
-def test_fp8_block_scaled_grouped_gemm(swiglu):
+def test_fp8_block_scaled_grouped_gemm(swiglu, tile):
     torch.manual_seed(2)
     counts, N, K = [150, 0, 128, 300], 256, 1024
     ends, rows = _segments(counts, 128)
@@ -73,7 +79,7 @@ def test_fp8_block_scaled_grouped_gemm(swiglu):
     scale = torch.rand(rows, device="cuda") + 0.5
     # a column-major scale view, the layout worker_receive can return
     a_scale_cm = a_scale.t().contiguous().t()
-    out = gg.grouped_gemm(a, w, ends.cuda(), 128, swiglu=swiglu, row_scale=scale, a_scale=a_scale_cm, w_scale=w_scale)
+    out = gg.grouped_gemm(a, w, ends.cuda(), 128, swiglu=swiglu, row_scale=scale, a_scale=a_scale_cm, w_scale=w_scale, tile=tile)
     torch.cuda.synchronize()
     ref = gg.reference_grouped_gemm(a, w, ends, 128, swiglu=swiglu, row_scale=scale, a_scale=a_scale, w_scale=w_scale)
     starts = gg.segment_starts(ends, 128).tolist()
@@ -136,3 +142,8 @@ def test_fp8_row_quantiser_matches_torch():
     bound = xf.abs() * 0.0625 + s[:257, :, None] * 2.0 ** -9 + 1e-30
     assert ((dq - xf).abs() <= bound).all()
     assert (dq[7] == 0).all()
+
+
+def test_unknown_tile_is_rejected():
+    with pytest.raises(ValueError):
+        gg.grouped_gemm(torch.zeros(1), torch.zeros(1), torch.zeros(1), 128, tile="tall")

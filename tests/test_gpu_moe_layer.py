@@ -18,8 +18,9 @@ def _dequant_blocks(w, scale):
     return (w.float().view(E, N // 128, 128, K // 128, 128) * scale.view(E, N // 128, 1, K // 128, 1)).reshape(E, N, K)
 
 
+@pytest.mark.parametrize("tile", ["wide", "swapped"])
 @pytest.mark.parametrize("payload,mode,down", [("bf16", "bf16", "bf16"), ("fp8", "fp8", "fp8"), ("bf16", "fp8", "fp8"), ("fp8", "fp8", "bf16")])
-def test_moe_layer_matches_dense_reference(payload, mode, down):
+def test_moe_layer_matches_dense_reference(payload, mode, down, tile):
     from afdep_b200.parallel.loopback import LoopbackWorld
 
     hidden, inter, experts, top_k, ffn, attn, tokens = 512, 256, 8, 2, 2, 2, 96
@@ -34,7 +35,7 @@ def test_moe_layer_matches_dense_reference(payload, mode, down):
 
         def expert(i, rec):
             kept[i] = rec
-            return run_experts(rec, weights[i], cfg.expert_alignment)
+            return run_experts(rec, weights[i], cfg.expert_alignment, tile=tile)
 
         outs, received = world.exchange(dev, expert)
         torch.cuda.synchronize()
@@ -42,7 +43,7 @@ def test_moe_layer_matches_dense_reference(payload, mode, down):
             b.check()
         # the kernels' rows against the fp32 reference of the same MLP on the same received rows
         for i, rec in enumerate(received):
-            got = run_experts(rec, weights[i], cfg.expert_alignment).float()
+            got = run_experts(rec, weights[i], cfg.expert_alignment, tile=tile).float()
             want = reference_experts(rec, weights[i], cfg.expert_alignment).float()
             ends = rec.recv_count_psum.cpu().tolist()
             start = 0
