@@ -94,3 +94,35 @@ def _pending_close(rank, world):
 
 def test_close_refuses_pending_exchange_on_every_rank():
     run_ranks(_pending_close, 4)
+
+
+def _withheld_reply(rank, world):
+    """Failure made on the host: FFN rank 0 receives and then never replies.  The attention
+    ranks are waiting for its rows; their next collective call must fail within the group's
+    timeout instead of blocking for good, and every process must still be able to leave."""
+    import datetime
+
+    import torch.distributed as dist
+
+    group = dist.new_group(list(range(world)), backend="gloo", timeout=datetime.timedelta(seconds=4))
+    cfg = Config(8, 256, 8, 2, 2, 2, expert_alignment=1)
+    buf = Buffer(group=group, config=cfg, backend="gloo")
+    batch = synthetic.exact_batch(cfg, 8, 0, 0)
+    if buf.role == "attention":
+        buf.source_dispatch(*batch[:3], bucket=8)
+        with pytest.raises(RuntimeError):
+            buf.source_collect()           # rows of FFN rank 0 never come
+    else:
+        rec = buf.worker_receive(bucket=8)
+        if buf.role_rank == 1:
+            rows = oracle.synthetic_expert_rows(cfg, 1, rec.recv_x, rec.recv_scale, rec.recv_topk_weights, rec.recv_count_psum)
+            try:
+                buf.worker_reply(rows, rec.receipt)
+            except RuntimeError:
+                pass      # its receivers were stuck behind the failed rank: a bounded failure too, not a hang
+        # role rank 0 "fails" here: it keeps its receipt and says nothing
+    # the Buffer is not closed (its exchange cannot complete); the job's own group is still healthy
+
+
+def test_withheld_reply_fails_within_the_group_timeout():
+    run_ranks(_withheld_reply, 4, timeout=120)
