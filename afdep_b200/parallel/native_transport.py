@@ -158,6 +158,15 @@ class NativeTransport:
             if t is not None and t.numel():
                 t.record_stream(self._comm_stream)
         current.wait_stream(self._comm_stream)
+        # results were allocated while the communication stream was current but are consumed on
+        # the caller's stream: tell the allocator, or a freed block could be reused too early
+        stack = [out]
+        while stack:
+            item = stack.pop()
+            if isinstance(item, (tuple, list)):
+                stack.extend(item)
+            elif isinstance(item, torch.Tensor) and item.is_cuda and item.numel():
+                item.record_stream(current)
         return out
 
     def check_device(self) -> None:
