@@ -27,7 +27,6 @@ from dataclasses import dataclass
 import torch
 
 from ..buffer import Buffer, ReceiveResult
-from ..config import Config
 from ..ops import grouped_gemm as gg
 
 
