@@ -664,6 +664,42 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         d["stream_memops"] = true;
         return d;
     });
+    // Heap layout and launch shapes as plain numbers, for checks that need no GPU: offsets,
+    // alignments and shared-memory budgets are pure functions of the configuration.
+    m.def("geometry", [](int ffn, int attn, int hidden, int top_k, int num_experts, int capacity, bool fp8, int alignment, int64_t aux_bytes) {
+        const afdep::Geometry g = afdep::make_geometry(ffn, attn, hidden, top_k, num_experts, capacity, fp8 ? 1 : 0, alignment, (size_t)aux_bytes);
+        py::dict d;
+        d["payload_bytes"] = g.payload_bytes;
+        d["scale_bytes"] = g.scale_bytes;
+        d["meta_bytes"] = g.meta_bytes;
+        d["meta_off"] = g.meta_off;
+        d["rec_bytes"] = g.rec_bytes;
+        d["row_bytes"] = g.row_bytes;
+        d["experts_local"] = g.experts_local;
+        d["cnt_stride"] = afdep::cnt_stride(g);
+        d["ctrl_bytes"] = (int64_t)g.ctrl_bytes;
+        d["aux_off"] = (int64_t)g.aux_off;
+        d["aux_bytes"] = (int64_t)g.aux_bytes;
+        d["f_cnt"] = (int64_t)g.f_cnt;
+        d["f_slot_flag"] = (int64_t)g.f_slot_flag;
+        d["f_stage"] = (int64_t)g.f_stage;
+        d["f_reply"] = (int64_t)g.f_reply;
+        d["f_bytes"] = (int64_t)g.f_bytes;
+        d["a_reply_flag"] = (int64_t)g.a_reply_flag;
+        d["a_bytes"] = (int64_t)g.a_bytes;
+        return d;
+    });
+    m.def("launch_shapes", [](int ffn, int attn, int hidden, int top_k, int num_experts, int capacity, bool fp8, int alignment, int tokens,
+                              int num_sms, int collect_sms, int ffn_sms, int max_smem) {
+        const afdep::Geometry g = afdep::make_geometry(ffn, attn, hidden, top_k, num_experts, capacity, fp8 ? 1 : 0, alignment, 0);
+        auto pack = [](const afdep::LaunchShape& s) { return py::make_tuple(s.ctas, s.warps, s.smem_bytes); };
+        py::dict d;
+        d["dispatch"] = pack(afdep::dispatch_shape(g, tokens, num_sms, max_smem));
+        d["receive"] = pack(afdep::receive_shape(g, ffn_sms, max_smem));
+        d["reply"] = pack(afdep::reply_shape(g, ffn_sms, max_smem));
+        d["collect"] = pack(afdep::collect_shape(g, tokens, collect_sms, max_smem));
+        return d;
+    });
     m.def("grouped_gemm", &afdep::grouped_gemm, py::arg("a"), py::arg("w"), py::arg("ends"), py::arg("alignment"),
           py::arg("swiglu") = false, py::arg("row_scale") = py::none(), py::arg("a_scale") = py::none(),
           py::arg("w_scale") = py::none(), py::arg("out") = py::none(), py::arg("ctas") = 0, py::arg("quantize_out") = false, py::arg("swapped") = false);
