@@ -13,7 +13,7 @@ import json
 import platform
 
 from . import __version__
-from ._native import library_path, load_native, resolve_nvcc, source_digest, stale_libraries
+from ._native import build_signature, library_path, load_native, resolve_nvcc, source_digest, stale_libraries, toolchain_signature
 
 
 def report(build: bool) -> dict:
@@ -21,6 +21,8 @@ def report(build: bool) -> dict:
         "afdep_b200": __version__,
         "platform": platform.platform(),
         "source_digest": source_digest(),
+        "build_signature": build_signature(),
+        "toolchain": toolchain_signature(),
         "native_library": str(library_path()),
         "native_library_built": library_path().exists(),
         "stale_libraries": [p.name for p in stale_libraries()],

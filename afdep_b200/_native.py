@@ -1,8 +1,8 @@
 """Build and load the sm_100a extension, in-tree and content-addressed.
 
 The native sources under ``csrc/`` are compiled ahead of time into
-``afdep_b200/_lib/_afdep_native_<digest>.so`` where ``<digest>`` hashes every source file
-and the build flags.  A matching library is simply imported; otherwise the library is
+``afdep_b200/_lib/_afdep_native_<digest>.so`` where ``<digest>`` hashes every source file,
+the build flags and the toolchain (torch build, Python ABI, nvcc release).  A matching library is simply imported; otherwise the library is
 (re)built under a file lock, so the ranks of one job do not compile concurrently, and
 published with an atomic rename.  There is no run-time kernel JIT: shapes are run-time
 arguments of a fixed set of kernels.
@@ -15,7 +15,9 @@ module does not import torch.
 from __future__ import annotations
 
 import fcntl
+import functools
 import hashlib
+import importlib.metadata
 import importlib.util
 import os
 import shutil
@@ -62,8 +64,43 @@ def source_digest() -> str:
     return h.hexdigest()
 
 
+@functools.lru_cache(maxsize=1)
+def _nvcc_version() -> str:
+    try:
+        out = subprocess.run([resolve_nvcc(), "--version"], capture_output=True, text=True, timeout=30).stdout
+        return out.strip().splitlines()[-1] if out.strip() else "unknown"
+    except (OSError, RuntimeError, subprocess.SubprocessError):
+        return "unavailable"
+
+
+def toolchain_signature() -> dict:
+    """What the binary depends on besides the sources: the torch build it links against (its
+    version string, with the CUDA tag, also fixes the C++ ABI of libtorch), the Python ABI of the
+    extension module and the nvcc release.  Read without importing torch.  The reference's
+    build signature covers the same ground (afdep/_build.py:153-184)."""
+    try:
+        torch_version = importlib.metadata.version("torch")
+    except importlib.metadata.PackageNotFoundError:
+        torch_version = "absent"
+    return {
+        "torch": torch_version,
+        "python_abi": sysconfig.get_config_var("SOABI") or sys.version.split()[0],
+        "nvcc": _nvcc_version(),
+        "arch": "sm_100a",
+    }
+
+
+def build_signature() -> str:
+    """SHA-256 over the source digest and the toolchain: a torch, Python or CUDA upgrade
+    changes the library's name, so a stale binary is never picked up."""
+    h = hashlib.sha256(source_digest().encode())
+    for key, value in sorted(toolchain_signature().items()):
+        h.update(f"{key}={value}\0".encode())
+    return h.hexdigest()
+
+
 def module_name() -> str:
-    return f"_afdep_native_{source_digest()[:16]}"
+    return f"_afdep_native_{build_signature()[:16]}"
 
 
 def library_path() -> Path:
@@ -98,25 +135,21 @@ def _run(cmd: list[str]) -> None:
         raise RuntimeError("native build step failed:\n  " + " ".join(cmd) + "\n" + proc.stdout + proc.stderr)
 
 
-def extra_include_dirs() -> list[str]:
-    """CUTLASS/CuTe headers are not used; kept as a hook for local experiments."""
-    return []
-
-
-def build(verbose: bool = False) -> Path:
-    """Compile every ``.cu``/``.cpp`` for sm_100a and link the extension; returns its path."""
+def build(verbose: bool = False, force: bool = False) -> Path:
+    """Compile every ``.cu``/``.cpp`` for sm_100a and link the extension; returns its path.
+    ``force=True`` rebuilds even when a library with the current signature exists."""
     import torch
     from torch.utils import cpp_extension
 
     target = library_path()
-    if target.exists():
+    if target.exists() and not force:
         return target
     LIB_DIR.mkdir(parents=True, exist_ok=True)
     name = module_name()
     with open(LIB_DIR / ".build.lock", "w") as lock:
         fcntl.flock(lock, fcntl.LOCK_EX)
         try:
-            if target.exists():
+            if target.exists() and not force:
                 return target
             work = LIB_DIR / f"build-{name}-{os.getpid()}"
             work.mkdir(parents=True, exist_ok=True)
@@ -132,7 +165,7 @@ def build(verbose: bool = False) -> Path:
                     continue
                 obj = work / (src.stem + ".o")
                 objects.append(str(obj))
-                inc = [f"-I{d}" for d in includes + extra_include_dirs()]
+                inc = [f"-I{d}" for d in includes]
                 if src.suffix == ".cu":
                     cmd = [nvcc, *NVCC_FLAGS, *inc, "-c", str(src), "-o", str(obj)]
                 else:

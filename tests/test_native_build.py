@@ -57,3 +57,14 @@ def test_every_kernel_source_targets_sm100a_and_never_traps():
         text = p.read_text()
         code = "\n".join(line.split("//")[0] for line in text.splitlines())
         assert "__trap" not in code and "asm(\"trap" not in code and "assert(" not in code.replace("static_assert(", ""), p.name
+
+
+def test_build_signature_changes_with_the_toolchain(monkeypatch):
+    base = _native.build_signature()
+    assert base != _native.source_digest() and _native.module_name().endswith(base[:16])
+    sig = dict(_native.toolchain_signature())
+    assert {"torch", "python_abi", "nvcc", "arch"} <= set(sig)
+    for key in ("torch", "python_abi", "nvcc"):
+        changed = dict(sig, **{key: sig[key] + "-other"})
+        monkeypatch.setattr(_native, "toolchain_signature", lambda changed=changed: changed)
+        assert _native.build_signature() != base, key
