@@ -456,6 +456,27 @@ class Buffer:
         self._tensor(rows, self._t.bfloat16, receipt.recv_shape)
         self.transport.combine(rows, receipt)
 
+    def worker_serve_fused(self, weights, *, bucket: int):
+        """FFN, native transport: receive, SwiGLU experts and reply of one exchange as one call.
+
+        ``weights`` is an ``afdep_b200.models.moe_layer.ExpertWeights``.  The received rows are
+        never copied into an expert-major ``recv_x``: the gate|up GEMM gathers them from the wire
+        records as their arrival flags land.  Returns ``(ReceiveResult, rows)`` where ``recv_x`` and
+        ``recv_scale`` are ``None`` and ``rows`` are the BF16 rows that went into the reply.  An
+        extension: the reference leaves the experts to its caller (README.md:54-56)."""
+        self._check_role("ffn")
+        t = self.transport
+        if t._pending is not None:
+            raise RuntimeError("Complete the previous exchange before dispatch")
+        if type(bucket) is not int or not 0 < bucket <= self.config.capacity_tokens_per_rank:
+            raise ValueError("bucket must be positive and within capacity")
+        if not hasattr(self._t, "worker_mlp_fused"):
+            raise RuntimeError("the fused expert path needs the native transport")
+        t._raise_device_status()
+        psum, recv_w, recv_src, rows = self._t.worker_mlp_fused(weights, bucket=bucket)
+        handle = DispatchHandle(t.num_experts, bucket, t._num_sms(), tuple(rows.shape), 0, recv_src, t._owner)
+        return ReceiveResult(None, None, recv_w, psum, [], handle), rows
+
     def check(self) -> None:
         """Raise now if a kernel of this Buffer has reported an error (does not synchronise)."""
         self.transport._raise_device_status()

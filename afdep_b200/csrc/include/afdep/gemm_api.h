@@ -34,10 +34,12 @@ struct GroupedGemmArgs {
 int grouped_gemm_smem_bytes();
 cudaError_t launch_grouped_gemm(const CUtensorMap& map_a, const CUtensorMap& map_w, const GroupedGemmArgs& args, int ctas,
                                 cudaStream_t stream);
-// The same product for small batches (kernels/grouped_gemm_swapped.cu): weight rows are the MMA's M
-// operand (tensor map boxes of 128 rows), tokens its 64-wide N operand (boxes of 64 rows).  No
-// quantised output.
-cudaError_t launch_grouped_gemm_swapped(const CUtensorMap& map_w, const CUtensorMap& map_a, const GroupedGemmArgs& args, int ctas,
-                                        cudaStream_t stream);
+// Host-visible error word of this device's GEMM launches (mapped pinned memory): `device` is the
+// pointer kernels write through, `host` the one the runtime polls.  Allocated on first use.
+struct GemmErrorWord {
+    int* device;
+    volatile int* host;
+};
+GemmErrorWord gemm_error_word(int device_ordinal);
 
 }  // namespace afdep

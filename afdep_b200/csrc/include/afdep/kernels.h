@@ -85,6 +85,8 @@ struct ReceiveArgs {
     int rows_cap;
     int layout_ready;       // 1: launch_ffn_layout already ran for this exchange
     int write_host_counts;  // layout kernel only
+    unsigned* tile_cnt;     // layout kernel only, optional: per-tile row counters of the fused expert path, zeroed here
+    int tile_cnt_n;
 };
 
 struct LaunchShape {

@@ -30,8 +30,25 @@
  *     it.  Serialise them.
  *   - Nothing here calls cudaMalloc, cudaFree or any routine that allocates.
  *
- * Returns 0 on success or one of the codes below; `afdep_route_layout_noalloc_error`
- * gives the text of the calling thread's last failure.
+ *   - The cached address belongs to the device's context at the time of that first call.
+ *     After cudaDeviceReset (or any other teardown of that context) the cache is stale:
+ *     do not call this entry point again in such a process.
+ *
+ * What the return value covers, and what it does not.  A return of 0 means the arguments
+ * were accepted and the kernel was launched; like any launch, the work itself finishes later
+ * on `stream`.  Two outcomes only show in the outputs, after the stream has been synchronised:
+ *   - An illegal token (an id outside [-1, num_experts), or an expert named twice) is not an
+ *     error code.  All of that token's choices come back as route_e == -1, its tok_slot
+ *     entries as -1, and it is left out of the counts; every other token is laid out as
+ *     usual.  (The number of such tokens is kept in scratch the caller cannot read: compare
+ *     route_e with ids if you need it.)
+ *   - If the CTAs' wait on one another runs out of its five-second budget (which needs a GPU
+ *     so oversubscribed that the grid is not resident together), every entry of counts[]
+ *     comes back as -1 and route_pos / tok_slot hold CTA-local values that must not be used.
+ *     A caller that cannot tolerate this checks counts[0] >= 0 before consuming the rest.
+ *
+ * Returns 0 when the launch was issued, or one of the codes below; the function
+ * `afdep_route_layout_noalloc_error` gives the text of the calling thread's last failure.
  */
 #pragma once
 

@@ -112,5 +112,51 @@ __device__ __forceinline__ void tmem_ld_wait_on(uint32_t (&r)[32]) {
                  : "memory");
 }
 
+// ---- hardware block scaling (kind::mxf8f6f4.block_scale) ---------------------------------
+// The tensor core multiplies every 32-deep slice of K by 2^(sfa - 127) * 2^(sfb - 127), where
+// sfa / sfb are one byte (UE8M0, a bare exponent) per row of A / per column of B, read from
+// tensor memory.  Layout of a scale block in tensor memory, per 32-lane quarter and repeated in
+// all four quarters: 32-bit column j of lane l holds the four bytes of row (or column) 32 * j + l;
+// the instruction descriptor's a_sf_id / b_sf_id pick which of the four bytes an MMA uses.
+// 128 rows of A take 4 columns, 256 columns of B take 8.
+//
+// Instruction descriptor: A and B e4m3, both K-major, fp32 accumulate, UE8M0 scales.
+__host__ __device__ constexpr uint32_t instr_desc_block_scaled(uint32_t m, uint32_t n, uint32_t a_sf_id, uint32_t b_sf_id) {
+    return (b_sf_id << 4) | ((n >> 3) << 17) | (1u << 23) | ((m >> 4) << 24) | (a_sf_id << 29);
+}
+__device__ __forceinline__ void mma_mxfp8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate,
+                                          uint32_t sfa_tmem, uint32_t sfb_tmem) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+}
+// The biased exponent byte of a float that is an exact power of two (UE8M0 of that scale).
+__device__ __forceinline__ uint32_t ue8m0_of_pow2(float s) { return (__float_as_uint(s) >> 23) & 0xffu; }
+
+// ---- registers -> TMEM (whole warp; a warp reaches the 32 lanes of quarter warp_id % 4) --------
+__device__ __forceinline__ void tmem_st4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&v)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(v[0]), "r"(v[1]),
+                 "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// ---- 16-byte asynchronous copies (gathered operand rows) ---------------------------------------
+// global -> shared, bypassing L1; `src_bytes` = 0 writes sixteen zero bytes instead (padding rows).
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(ptx::smem_addr(smem_dst)), "l"(gsrc), "r"(src_bytes) : "memory");
+}
+// Arrives once on `bar` when every cp.async this thread has issued so far has landed; the
+// barrier's expected count must include this arrival.
+__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(ptx::smem_addr(bar)) : "memory");
+}
+
 }  // namespace tc
 }  // namespace afdep

@@ -388,12 +388,19 @@ LaunchShape dispatch_shape(const Geometry& g, int tokens, int num_sms, int max_s
 cudaError_t launch_dispatch(const RankCtx& c, const AttnWs& ws, const DispatchArgs& a, LaunchShape s,
                             cudaStream_t stream) {
     const DispatchPlan p = plan_dispatch(c.g, a.T, s.ctas);
-    switch (p.nb) {
-        case 4: dispatch_kernel<4><<<p.ctas, p.warps * 32, p.smem_bytes, stream>>>(c, ws, a, p); break;
-        case 3: dispatch_kernel<3><<<p.ctas, p.warps * 32, p.smem_bytes, stream>>>(c, ws, a, p); break;
-        default: dispatch_kernel<2><<<p.ctas, p.warps * 32, p.smem_bytes, stream>>>(c, ws, a, p); break;
-    }
-    return cudaGetLastError();
+    const void* fn = p.nb == 4 ? reinterpret_cast<const void*>(dispatch_kernel<4>)
+                   : p.nb == 3 ? reinterpret_cast<const void*>(dispatch_kernel<3>)
+                               : reinterpret_cast<const void*>(dispatch_kernel<2>);
+    void* params[] = {const_cast<RankCtx*>(&c), const_cast<AttnWs*>(&ws), const_cast<DispatchArgs*>(&a), const_cast<DispatchPlan*>(&p)};
+    // With the layout split over the CTAs, a CTA waits on the look-back aggregates and on the
+    // "chunk final" words of other CTAs, so all of them must be on the GPU together.  A
+    // cooperative launch guarantees that (it starts only when the whole grid fits beside what is
+    // already running, and a grid that can never fit is refused here, on the host) -- the
+    // reference launches its dispatch the same way (csrc/kernels/elastic/dispatch.hpp:306).
+    // When every CTA ranks all tokens itself there is nothing to wait for and a plain launch does.
+    if (!p.redundant && p.ctas > 1)
+        return cudaLaunchCooperativeKernel(fn, dim3(p.ctas), dim3(p.warps * 32), params, (size_t)p.smem_bytes, stream);
+    return cudaLaunchKernel(fn, dim3(p.ctas), dim3(p.warps * 32), params, (size_t)p.smem_bytes, stream);
 }
 
 cudaError_t configure_dispatch(int max_smem) {

@@ -18,6 +18,7 @@
 // dispatch_copy_epilogue.cuh, combine.cuh; csrc/elastic/buffer.hpp:994-1041).
 #include <cuda_bf16.h>
 
+#include "afdep/ffn_layout.cuh"
 #include "afdep/kernels.h"
 #include "afdep/status.cuh"
 
@@ -27,14 +28,6 @@ namespace {
 
 constexpr int kBarBytes = 512;
 constexpr int kMaxWarps = 16;
-
-struct LayoutSmem {
-    int row_base[kMaxRanks * kMaxExpertsLocal];   // [attn][experts_local]
-    int tot[kMaxExpertsLocal];
-    int start[kMaxExpertsLocal];
-    int rec_prefix[kMaxRanks + 1];
-    int dead;
-};
 
 __device__ __forceinline__ int align_up_dev(int v, int a) { return (v + a - 1) / a * a; }
 
@@ -153,46 +146,6 @@ __device__ void publish_layout(const RankCtx& c, const FfnWs& ws, const ReceiveA
     for (int i = threadIdx.x; i <= A; i += blockDim.x) ws.rec_prefix[i] = L.rec_prefix[i];
 }
 
-__device__ void load_layout(const RankCtx& c, const FfnWs& ws, LayoutSmem& L) {
-    const Geometry& g = c.g;
-    const int A = g.attn, EL = g.experts_local;
-    for (int i = threadIdx.x; i < A * EL; i += blockDim.x) L.row_base[i] = ws.row_base[i];
-    for (int i = threadIdx.x; i <= A; i += blockDim.x) L.rec_prefix[i] = ws.rec_prefix[i];
-    if (threadIdx.x == 0) L.dead = 0;
-    __syncthreads();
-}
-
-
-// Dense work index -> (source, slot), ordered by slot first and source second, so that the
-// records of all sources advance together: every attention rank starts seeing its rows (and
-// its reply flags) from the beginning of the kernel instead of one source after the other.
-__device__ __forceinline__ void locate_striped(const LayoutSmem& L, int A, int j, int& a, int& slot) {
-    // cum(s) = number of records with slot < s = sum over sources of min(count, s)
-    int lo = 0, hi = 1;
-    for (int q = 0; q < A; ++q) hi = max(hi, L.rec_prefix[q + 1] - L.rec_prefix[q]);
-    // largest s with cum(s) <= j
-    while (hi - lo > 1) {
-        const int mid = (lo + hi) >> 1;
-        int cum = 0;
-        for (int q = 0; q < A; ++q) cum += min(L.rec_prefix[q + 1] - L.rec_prefix[q], mid);
-        if (cum <= j) lo = mid; else hi = mid;
-    }
-    int cum = 0;
-    for (int q = 0; q < A; ++q) cum += min(L.rec_prefix[q + 1] - L.rec_prefix[q], lo);
-    int r = j - cum;            // r-th source (in rank order) that still has a record at this slot
-    slot = lo;
-    a = 0;
-    for (int q = 0; q < A; ++q) {
-        if (L.rec_prefix[q + 1] - L.rec_prefix[q] > lo) {
-            if (r == 0) {
-                a = q;
-                break;
-            }
-            --r;
-        }
-    }
-}
-
 // Stand-alone layout pass, used when the host wants exact counts before it allocates the
 // receive tensors.  Writes aligned per-expert counts and a sequence number to mapped host
 // memory; the receive kernel that follows is launched with layout_ready = 1.
@@ -201,6 +154,8 @@ __global__ void __launch_bounds__(256, 1) ffn_layout_kernel(const RankCtx c, con
     const Geometry& g = c.g;
     const unsigned ep = ptx::ld_acquire_gpu(&ws.epoch[0]) + 1u;
     const WaitCtx wc{c.status, c.poison, c.budget, c.rank, /*kernel=*/2};
+    if (r.tile_cnt != nullptr)
+        for (int i = threadIdx.x; i < r.tile_cnt_n; i += blockDim.x) r.tile_cnt[i] = 0u;
     const bool ok = compute_layout(c, wc, ep, L);
     if (ok) publish_layout(c, ws, r, L);
     __syncthreads();

@@ -25,6 +25,8 @@
 // tile never straddles two experts; tiles past an expert's last row are skipped, rows past it
 // inside the last tile are padding.  The reference library has no GEMM at all (callers bring
 // their own); this kernel is the expert path of the end-to-end benchmark.
+#include <mutex>
+
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 
@@ -433,16 +435,34 @@ constexpr int kSmemBytes = kStages * kStageBytes + (int)sizeof(Ctrl) + 1024;
 
 int grouped_gemm_smem_bytes() { return kSmemBytes; }
 
+GemmErrorWord gemm_error_word(int device_ordinal) {
+    static std::mutex mu;
+    static GemmErrorWord words[64] = {};
+    std::lock_guard<std::mutex> lock(mu);
+    if (device_ordinal < 0 || device_ordinal >= 64) return GemmErrorWord{nullptr, nullptr};
+    GemmErrorWord& w = words[device_ordinal];
+    if (w.host == nullptr) {
+        void* host = nullptr;
+        void* dev = nullptr;
+        if (cudaHostAlloc(&host, 64, cudaHostAllocMapped) != cudaSuccess) return GemmErrorWord{nullptr, nullptr};
+        *static_cast<int*>(host) = 0;
+        if (cudaHostGetDevicePointer(&dev, host, 0) != cudaSuccess) {
+            cudaFreeHost(host);
+            return GemmErrorWord{nullptr, nullptr};
+        }
+        w.host = static_cast<volatile int*>(host);
+        w.device = static_cast<int*>(dev);
+    }
+    return w;
+}
+
 cudaError_t launch_grouped_gemm(const CUtensorMap& map_a, const CUtensorMap& map_w, const GroupedGemmArgs& args, int ctas,
                                 cudaStream_t stream) {
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(grouped_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    // The attribute belongs to the current device's context, so it is set on every launch
+    // (a cheap call) rather than remembered per process.
+    cudaError_t e = args.fp8 ? cudaFuncSetAttribute(grouped_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes)
+                             : cudaFuncSetAttribute(grouped_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return e;
     if (args.fp8)
         grouped_gemm_kernel<true><<<ctas, cta_threads(true), kSmemBytes, stream>>>(map_a, map_w, args);
     else

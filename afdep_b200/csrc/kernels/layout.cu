@@ -72,13 +72,10 @@ int route_layout_ctas(int tokens) {
 
 cudaError_t launch_route_layout(const long long* ids, int T, int K, int E, int F, void* scratch, int* route_e,
                                 int* route_pos, int* tok_slot, int* counts, long long budget, cudaStream_t stream) {
-    static bool configured = false;
     const int smem = route_layout_scratch_ints(kRouteLayoutWarps, F + E) * 4;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(route_layout_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
+    // per device context, so set on every launch instead of once per process
+    cudaError_t e = cudaFuncSetAttribute(route_layout_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    if (e != cudaSuccess) return e;
     route_layout_kernel<<<route_layout_ctas(T), kRouteLayoutWarps * 32, smem, stream>>>(
         ids, T, K, E, F, static_cast<unsigned char*>(scratch), route_e, route_pos, tok_slot, counts, budget);
     return cudaGetLastError();

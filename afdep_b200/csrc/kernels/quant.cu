@@ -15,7 +15,7 @@ namespace {
 
 __global__ void __launch_bounds__(256) quantize_rows_kernel(const __nv_bfloat16* __restrict__ x, unsigned char* __restrict__ q,
                                                             float* __restrict__ scale, int rows, int K, long long ss0, long long ss1,
-                                                            const int* __restrict__ limit) {
+                                                            const int* __restrict__ limit, int pow2) {
     const int lane = threadIdx.x & 31;
     const int groups = K / 128;
     const long long total = (long long)rows * groups;
@@ -32,7 +32,13 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const __nv_bfloat16*
         float amax = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y)));
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
-        const float s = fmaxf(amax, 1e-12f) / 448.f;
+        float s = fmaxf(amax, 1e-12f) / 448.f;
+        if (pow2) {       // round the scale up to a power of two: exact as an exponent byte
+            const unsigned bits = __float_as_uint(s);
+            unsigned e = (bits >> 23) & 0xffu;
+            if (bits & 0x7fffffu) ++e;
+            s = __uint_as_float(min(max(e, 1u), 253u) << 23);
+        }
         const float inv = 1.f / s;
         const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a.x * inv, a.y * inv), __NV_SATFINITE, __NV_E4M3);
         const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(b.x * inv, b.y * inv), __NV_SATFINITE, __NV_E4M3);
@@ -44,10 +50,10 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const __nv_bfloat16*
 }  // namespace
 
 cudaError_t launch_quantize_rows(const void* x, void* q, float* scale, int rows, int K, long long ss0, long long ss1,
-                                 const int* limit, int ctas, cudaStream_t stream) {
+                                 const int* limit, bool pow2, int ctas, cudaStream_t stream) {
     if (rows == 0) return cudaSuccess;
     quantize_rows_kernel<<<ctas, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<unsigned char*>(q), scale, rows,
-                                                   K, ss0, ss1, limit);
+                                                   K, ss0, ss1, limit, pow2 ? 1 : 0);
     return cudaGetLastError();
 }
 

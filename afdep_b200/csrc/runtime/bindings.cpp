@@ -20,6 +20,7 @@
 #include <thread>
 
 #include "afdep/aux_api.h"
+#include "afdep/expert_gemm_api.h"
 #include "afdep/gemm_api.h"
 #include "afdep/kernels.h"
 #include "afdep/quant_api.h"
@@ -57,6 +58,39 @@ SymmetricHeap::Mode parse_mode(const std::string& m) {
 }
 
 }  // namespace
+
+namespace {
+
+// Tensor map of a row-major [rows, cols] matrix with 128-byte-swizzled boxes of `box_rows`
+// rows by 128 bytes, the tile shape the grouped GEMM's shared-memory descriptors expect.
+CUtensorMap make_tile_map(const void* base, int64_t rows, int64_t cols, int elem_bytes, int box_rows) {
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)cols * (cuuint64_t)elem_bytes};
+    const cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1u, 1u};
+    const CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    drv_check(AFDEP_DRV(cuTensorMapEncodeTiled)(&map, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+                                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE),
+              "cuTensorMapEncodeTiled");
+    return map;
+}
+
+}  // namespace
+
+// The device's GEMM error word, after raising for any failure an earlier launch left in it.  A
+// kernel whose bounded wait ran out sets the word and returns with its output incomplete; the
+// next GEMM call on that device (or gemm_check) reports it.
+int* checked_gemm_error_word(int device) {
+    const GemmErrorWord w = gemm_error_word(device);
+    TORCH_CHECK(w.host != nullptr, "could not allocate the GEMM error word");
+    if (*w.host != 0) {
+        *w.host = 0;
+        throw std::runtime_error("an earlier expert GEMM on this device gave up on a bounded wait; its output is incomplete");
+    }
+    return w.device;
+}
 
 class NativeBuffer {
 public:
@@ -295,6 +329,134 @@ public:
         ++launches_;
     }
 
+
+    // Receive, experts and reply of one exchange without the expert-major copy of the received
+    // rows: a one-CTA layout pass, then the gate|up GEMM that indexes the wire records as they land
+    // and gathers its A rows straight from the staging region (SwiGLU in the epilogue), the down
+    // projection times the routing weight, and the reply kernel.  FP8 payloads need FP8 weights
+    // with power-of-two block scales; BF16 payloads need BF16 weights.
+    // Returns (psum, recv_weights, recv_src, rows sent back).
+    py::tuple worker_mlp_fused(const torch::Tensor& w_gate_up, const c10::optional<torch::Tensor>& w_gate_up_scale,
+                               const torch::Tensor& w_down, const c10::optional<torch::Tensor>& w_down_scale, int64_t rows_bound) {
+        live();
+        TORCH_CHECK(is_ffn_, "worker_mlp_fused runs on FFN ranks");
+        const int EL = geo_.experts_local, H = geo_.hidden;
+        const bool fp8 = geo_.fp8 != 0;
+        const auto wdt = fp8 ? torch::kFloat8_e4m3fn : torch::kBFloat16;
+        TORCH_CHECK(w_gate_up.is_cuda() && w_gate_up.dim() == 3 && w_gate_up.is_contiguous() && w_gate_up.scalar_type() == wdt &&
+                        w_gate_up.size(0) == EL && w_gate_up.size(2) == H && w_gate_up.size(1) % 256 == 0,
+                    "w_gate_up: [experts_local, 2*intermediate, hidden] in the payload's dtype");
+        const int64_t I = w_gate_up.size(1) / 2;
+        TORCH_CHECK(w_down.is_cuda() && w_down.dim() == 3 && w_down.is_contiguous() && w_down.scalar_type() == wdt && w_down.size(0) == EL &&
+                        w_down.size(1) == H && w_down.size(2) == I && I % 128 == 0,
+                    "w_down: [experts_local, hidden, intermediate] in the payload's dtype");
+        TORCH_CHECK(geo_.alignment % 128 == 0, "the fused expert path needs expert_alignment to be a multiple of 128");
+        if (fp8) {
+            TORCH_CHECK(w_gate_up_scale.has_value() && w_down_scale.has_value(), "FP8 experts need their block scales");
+            TORCH_CHECK(w_gate_up_scale->scalar_type() == torch::kFloat32 && w_gate_up_scale->is_contiguous() &&
+                            w_gate_up_scale->numel() == (int64_t)EL * (2 * I / 128) * (H / 128),
+                        "w_gate_up_scale: fp32 [experts_local, 2I/128, H/128]");
+            TORCH_CHECK(w_down_scale->scalar_type() == torch::kFloat32 && w_down_scale->is_contiguous() &&
+                            w_down_scale->numel() == (int64_t)EL * (H / 128) * (I / 128),
+                        "w_down_scale: fp32 [experts_local, H/128, I/128]");
+        }
+        const int64_t rows = rows_bound;
+        auto dev = torch::TensorOptions().device(torch::kCUDA, device_);
+        auto psum = torch::empty({EL}, dev.dtype(torch::kInt32));
+        auto recv_w = torch::empty({rows}, dev.dtype(torch::kFloat32));
+        auto recv_src = torch::empty({rows, 2}, dev.dtype(torch::kInt32));
+        auto row_rec = torch::empty({rows}, dev.dtype(torch::kInt32));
+        const int64_t n_tiles = rows / 128 + 1;
+        if (!tile_cnt_.defined() || tile_cnt_.numel() < n_tiles) tile_cnt_ = torch::zeros({n_tiles}, dev.dtype(torch::kInt32));
+        auto out = torch::empty({rows, H}, dev.dtype(torch::kBFloat16));
+        cudaStream_t st = stream();
+
+        ReceiveArgs r{};
+        r.psum = psum.data_ptr<int>();
+        r.expert_stats = expert_stats_.defined() ? reinterpret_cast<long long*>(expert_stats_.data_ptr<int64_t>()) : nullptr;
+        r.rows_cap = (int)rows;
+        r.tile_cnt = reinterpret_cast<unsigned*>(tile_cnt_.data_ptr<int>());
+        r.tile_cnt_n = (int)n_tiles;
+        rt_check(launch_ffn_layout(ctx_, fws_, r, st), "layout launch");
+        ++launches_;
+
+        int* err = checked_gemm_error_word(device_);
+        ExpertGemmArgs g{};
+        g.rows = (int)rows;
+        g.N = (int)(2 * I);
+        g.K = H;
+        g.experts = EL;
+        g.alignment = geo_.alignment;
+        g.ends = psum.data_ptr<int>();
+        g.mx = fp8 ? 1 : 0;
+        g.budget = ctx_.budget;
+        g.a_rows = reinterpret_cast<const unsigned char*>(heap_->local()) + geo_.f_stage;
+        g.a_pitch = geo_.rec_bytes;
+        g.row_rec = row_rec.data_ptr<int>();
+        g.a_scale_off = fp8 ? geo_.payload_bytes : -1;
+        g.w_scale = fp8 ? w_gate_up_scale->data_ptr<float>() : nullptr;
+        g.swiglu = 1;
+        g.ldc = (int)I;
+        g.error = err;
+        torch::Tensor h, h_scale;
+        if (fp8) {
+            h = torch::empty({rows, I}, dev.dtype(torch::kFloat8_e4m3fn));
+            h_scale = torch::empty({rows, I / 128}, dev.dtype(torch::kFloat32));
+            g.out_q = static_cast<unsigned char*>(h.data_ptr());
+            g.out_q_scale = h_scale.data_ptr<float>();
+            g.oqs0 = h_scale.stride(0);
+            g.oqs1 = h_scale.stride(1);
+        } else {
+            h = torch::empty({rows, I}, dev.dtype(torch::kBFloat16));
+            g.out = reinterpret_cast<__nv_bfloat16*>(h.data_ptr());
+        }
+        FusedReceive fr{};
+        fr.enabled = 1;
+        fr.c = ctx_;
+        fr.ws = fws_;
+        fr.row_rec = row_rec.data_ptr<int>();
+        fr.recv_w = recv_w.data_ptr<float>();
+        fr.recv_src = recv_src.data_ptr<int>();
+        fr.tile_cnt = reinterpret_cast<unsigned*>(tile_cnt_.data_ptr<int>());
+        fr.rows_cap = (int)rows;
+        const int elem = fp8 ? 1 : 2;
+        const int grid = ffn_sms_ < device_sms_ ? ffn_sms_ : device_sms_;
+        const CUtensorMap map_gu = make_tile_map(w_gate_up.data_ptr(), (int64_t)EL * 2 * I, H, elem, 256);
+        rt_check(launch_expert_gemm(map_gu, map_gu, g, /*gather=*/true, fr, grid, st), "fused gate/up GEMM launch");
+        ++launches_;
+
+        ExpertGemmArgs d{};
+        d.rows = (int)rows;
+        d.N = H;
+        d.K = (int)I;
+        d.experts = EL;
+        d.alignment = geo_.alignment;
+        d.ends = psum.data_ptr<int>();
+        d.mx = fp8 ? 1 : 0;
+        d.budget = ctx_.budget;
+        d.a_scale_off = -1;
+        if (fp8) {
+            d.a_scale = h_scale.data_ptr<float>();
+            d.a_scale_s0 = h_scale.stride(0);
+            d.a_scale_s1 = h_scale.stride(1);
+            d.w_scale = w_down_scale->data_ptr<float>();
+        }
+        d.out = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
+        d.ldc = H;
+        d.row_scale = recv_w.data_ptr<float>();
+        d.error = err;
+        const CUtensorMap map_h = make_tile_map(h.data_ptr(), rows, I, elem, 128);
+        const CUtensorMap map_dn = make_tile_map(w_down.data_ptr(), (int64_t)EL * H, I, elem, 256);
+        FusedReceive none{};
+        rt_check(launch_expert_gemm(map_h, map_dn, d, /*gather=*/false, none, device_sms_, st), "down GEMM launch");
+        ++launches_;
+
+        const LaunchShape s = reply_shape(geo_, ffn_sms_, max_smem_);
+        rt_check(launch_reply(ctx_, fws_, out.data_ptr(), (int)rows, s, st), "reply launch");
+        ++launches_;
+        return py::make_tuple(psum, recv_w, recv_src, out);
+    }
+
     // ---- status -----------------------------------------------------------------------
     py::dict status() {
         const volatile Status* s = static_cast<const volatile Status*>(host_block_);
@@ -419,6 +581,25 @@ public:
         return trace_;
     }
 
+    // Test hook: overwrite the payload regions of this rank's heap (wire records and reply rows on
+    // an FFN rank) with 0xFF bytes -- NaN in BF16, e4m3 and fp32 -- on the current stream.  Flags,
+    // counts and barrier words are left alone.  Only meaningful while no exchange is in flight on
+    // any rank; a stale read in a later exchange then shows up as NaN instead of plausible data.
+    void poison_payload() {
+        live();
+        if (!is_ffn_) return;
+        auto* base = static_cast<unsigned char*>(heap_->local());
+        rt_check(cudaMemsetAsync(base + geo_.f_stage, 0xFF, geo_.f_bytes - geo_.f_stage, stream()), "cudaMemsetAsync");
+    }
+
+    // Debugging knob: CTA budget of the next dispatches, not clamped to the device (up to the
+    // size of the look-back scratch).  A budget the GPU cannot hold at once makes the cooperative
+    // dispatch launch fail on the host instead of timing out on the device.
+    void set_dispatch_ctas(int n) {
+        TORCH_CHECK(n >= 1 && n <= max_dispatch_ctas(), "dispatch CTA budget out of range");
+        num_sms_ = n;
+    }
+
     int64_t launches() const { return launches_; }
     int resolved_num_sms() const { return num_sms_; }
     int device_sms() const { return device_sms_; }
@@ -434,6 +615,7 @@ public:
         agg_ = torch::Tensor();
         trace_ = torch::Tensor();
         expert_stats_ = torch::Tensor();
+        tile_cnt_ = torch::Tensor();
         heap_->release();
         if (host_block_) cudaFreeHost(host_block_);
         host_block_ = nullptr;
@@ -488,6 +670,7 @@ private:
     torch::Tensor flags_, scratch_, agg_, trace_;
     int64_t host_seq_ = 0, launches_ = 0;
     torch::Tensor expert_stats_;      // optional running per-expert row totals
+    torch::Tensor tile_cnt_;          // fused expert path: rows indexed per 128-row tile
     unsigned gathers_done_ = 0;       // all-gathers waited for outside graph capture
     bool gather_in_graph_ = false;    // an all-gather wait has been captured into a graph
 };
@@ -519,25 +702,7 @@ py::tuple route_layout(const torch::Tensor& ids, int64_t num_experts, int64_t ff
     return py::make_tuple(route_e, route_pos, tok_slot, counts);
 }
 
-namespace {
 
-// Tensor map of a row-major [rows, cols] matrix with 128-byte-swizzled boxes of `box_rows`
-// rows by 128 bytes, the tile shape the grouped GEMM's shared-memory descriptors expect.
-CUtensorMap make_tile_map(const void* base, int64_t rows, int64_t cols, int elem_bytes, int box_rows) {
-    CUtensorMap map;
-    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)cols * (cuuint64_t)elem_bytes};
-    const cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), (cuuint32_t)box_rows};
-    const cuuint32_t estr[2] = {1u, 1u};
-    const CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-    drv_check(AFDEP_DRV(cuTensorMapEncodeTiled)(&map, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
-                                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE),
-              "cuTensorMapEncodeTiled");
-    return map;
-}
-
-}  // namespace
 
 // out[rows, N or N/2] = A[rows, K] x W[e][N, K]^T per expert segment, on tcgen05.
 // a: bf16 or e4m3 [rows, K]; w: same dtype [experts, N, K]; ends: int32 [experts].
@@ -546,7 +711,7 @@ CUtensorMap make_tile_map(const void* base, int64_t rows, int64_t cols, int elem
 py::object grouped_gemm(const torch::Tensor& a, const torch::Tensor& w, const torch::Tensor& ends, int64_t alignment,
                         bool swiglu, const c10::optional<torch::Tensor>& row_scale,
                         const c10::optional<torch::Tensor>& a_scale, const c10::optional<torch::Tensor>& w_scale,
-                        const c10::optional<torch::Tensor>& out_opt, int64_t ctas, bool quantize_out, bool swapped) {
+                        const c10::optional<torch::Tensor>& out_opt, int64_t ctas, bool quantize_out) {
     TORCH_CHECK(a.is_cuda() && w.is_cuda() && ends.is_cuda(), "grouped_gemm needs CUDA tensors");
     TORCH_CHECK(a.dim() == 2 && w.dim() == 3 && a.is_contiguous() && w.is_contiguous(), "a [rows,K], w [experts,N,K], contiguous");
     TORCH_CHECK(a.scalar_type() == w.scalar_type(), "a and w must have the same dtype");
@@ -562,8 +727,8 @@ py::object grouped_gemm(const torch::Tensor& a, const torch::Tensor& w, const to
     const int64_t ldc = swiglu ? N / 2 : N;
     torch::Tensor out, out_q, out_q_scale;
     if (quantize_out) {
-        TORCH_CHECK(fp8 && swiglu && N % 256 == 0 && !out_opt.has_value() && !swapped,
-                    "quantize_out needs FP8 operands, swiglu, N a multiple of 256, the wide tile and no preallocated out");
+        TORCH_CHECK(fp8 && swiglu && N % 256 == 0 && !out_opt.has_value(),
+                    "quantize_out needs FP8 operands, swiglu, N a multiple of 256 and no preallocated out");
         out_q = torch::empty({rows, ldc}, torch::TensorOptions().dtype(torch::kFloat8_e4m3fn).device(a.device()));
         out_q_scale = torch::empty({rows, ldc / 128}, torch::TensorOptions().dtype(torch::kFloat32).device(a.device()));
     } else {
@@ -606,21 +771,116 @@ py::object grouped_gemm(const torch::Tensor& a, const torch::Tensor& w, const to
     int sms = 0;
     rt_check(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, a.get_device()), "device attribute");
     const int grid = ctas > 0 ? (int)ctas : sms;
-    if (swapped) {       // small batches: weights are the 128-row operand, tokens the 64-wide one
-        const CUtensorMap map_w = make_tile_map(w.data_ptr(), E * N, K, elem, 128);
-        const CUtensorMap map_a = make_tile_map(a.data_ptr(), rows, K, elem, 64);
-        rt_check(launch_grouped_gemm_swapped(map_w, map_a, g, grid, at::cuda::getCurrentCUDAStream().stream()), "grouped_gemm launch");
-        return result;
-    }
+    g.error = checked_gemm_error_word(a.get_device());
     const CUtensorMap map_a = make_tile_map(a.data_ptr(), rows, K, elem, 128);
     const CUtensorMap map_w = make_tile_map(w.data_ptr(), E * N, K, elem, 256);
     rt_check(launch_grouped_gemm(map_a, map_w, g, grid, at::cuda::getCurrentCUDAStream().stream()), "grouped_gemm launch");
     return result;
 }
 
+
+// The self-feeding expert GEMM (kernels/expert_gemm.cu) as a stand-alone operation.
+//   a          dense form: [rows, K] bf16 / e4m3.  Gathered form (row_index given): any contiguous
+//              2-D tensor whose row i starts with the K operand elements of "record" i; uint8 rows
+//              may carry the row's K/128 fp32 scales at byte offset a_scale_offset.
+//   row_index  optional int32 [rows]: record of every row of the row space (< 0: a row of zeros)
+//   FP8 operands need power-of-two scales (a_scale [rows, K/128] or in-record; w_scale).
+// Returns BF16 [rows, N or N/2], or with quantize_out (e4m3 [rows, N/2], fp32 power-of-two scales [rows, N/256]).
+py::object expert_gemm(const torch::Tensor& a, const torch::Tensor& w, const torch::Tensor& ends, int64_t alignment, bool swiglu,
+                       const c10::optional<torch::Tensor>& row_scale, const c10::optional<torch::Tensor>& a_scale,
+                       const c10::optional<torch::Tensor>& w_scale, const c10::optional<torch::Tensor>& out_opt, int64_t ctas,
+                       bool quantize_out, const c10::optional<torch::Tensor>& row_index, int64_t a_scale_offset) {
+    TORCH_CHECK(a.is_cuda() && w.is_cuda() && ends.is_cuda(), "expert_gemm needs CUDA tensors");
+    TORCH_CHECK(a.dim() == 2 && w.dim() == 3 && a.is_contiguous() && w.is_contiguous(), "a 2-D, w [experts,N,K], contiguous");
+    const bool fp8 = w.scalar_type() == torch::kFloat8_e4m3fn;
+    TORCH_CHECK(fp8 || w.scalar_type() == torch::kBFloat16, "bf16 or float8_e4m3fn weights");
+    const bool gather = row_index.has_value();
+    const int64_t E = w.size(0), N = w.size(1), K = w.size(2);
+    const int elem = fp8 ? 1 : 2;
+    int64_t rows;
+    if (gather) {
+        TORCH_CHECK(row_index->is_cuda() && row_index->scalar_type() == torch::kInt32 && row_index->is_contiguous() && row_index->dim() == 1,
+                    "row_index: contiguous int32 [rows] on the GPU");
+        rows = row_index->numel();
+        TORCH_CHECK(a.scalar_type() == w.scalar_type() || a.scalar_type() == torch::kUInt8, "gathered rows: the weights' dtype, or raw uint8 records");
+        TORCH_CHECK(a.size(1) * a.element_size() >= K * elem && (a.size(1) * a.element_size()) % 16 == 0, "records shorter than K, or pitch not a multiple of 16 bytes");
+    } else {
+        TORCH_CHECK(a.scalar_type() == w.scalar_type() && a.size(1) == K, "a must be [rows, K] of the weights' dtype");
+        rows = a.size(0);
+    }
+    TORCH_CHECK(K % 128 == 0 && N % 128 == 0, "K and N must be multiples of 128");
+    TORCH_CHECK(alignment % 128 == 0, "expert_alignment must be a multiple of 128 for the expert GEMM");
+    TORCH_CHECK(ends.scalar_type() == torch::kInt32 && ends.numel() == E && E <= kMaxExpertsLocal, "ends: int32 [experts]");
+    TORCH_CHECK(reinterpret_cast<uintptr_t>(a.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(w.data_ptr()) % 16 == 0, "operands must be 16-byte aligned");
+    c10::cuda::CUDAGuard guard(w.device());
+    const int64_t ldc = swiglu ? N / 2 : N;
+    torch::Tensor out, out_q, out_q_scale;
+    if (quantize_out) {
+        TORCH_CHECK(fp8 && swiglu && N % 256 == 0 && !out_opt.has_value(), "quantize_out needs FP8 operands, swiglu, N a multiple of 256 and no preallocated out");
+        out_q = torch::empty({rows, ldc}, torch::TensorOptions().dtype(torch::kFloat8_e4m3fn).device(w.device()));
+        out_q_scale = torch::empty({rows, ldc / 128}, torch::TensorOptions().dtype(torch::kFloat32).device(w.device()));
+    } else {
+        out = out_opt.has_value() ? *out_opt : torch::empty({rows, ldc}, torch::TensorOptions().dtype(torch::kBFloat16).device(w.device()));
+        TORCH_CHECK(out.scalar_type() == torch::kBFloat16 && out.is_contiguous() && out.size(0) == rows && out.size(1) == ldc, "out must be contiguous bf16 [rows, N or N/2]");
+    }
+    const py::object result = quantize_out ? py::object(py::make_tuple(out_q, out_q_scale)) : py::cast(out);
+    ExpertGemmArgs g{};
+    g.rows = (int)rows;
+    g.N = (int)N;
+    g.K = (int)K;
+    g.experts = (int)E;
+    g.alignment = (int)alignment;
+    g.ends = ends.data_ptr<int>();
+    g.mx = fp8 ? 1 : 0;
+    int khz = 0;
+    rt_check(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, w.get_device()), "device attribute");
+    g.budget = (long long)khz * 1000ll * 10ll;
+    g.a_scale_off = -1;
+    if (gather) {
+        g.a_rows = static_cast<const unsigned char*>(a.data_ptr());
+        g.a_pitch = a.size(1) * a.element_size();
+        g.row_rec = row_index->data_ptr<int>();
+    }
+    if (fp8) {
+        TORCH_CHECK(w_scale.has_value() && w_scale->scalar_type() == torch::kFloat32 && w_scale->is_contiguous() &&
+                        w_scale->numel() == E * (N / 128) * (K / 128), "w_scale: fp32 [experts, N/128, K/128]");
+        g.w_scale = w_scale->data_ptr<float>();
+        if (a_scale.has_value()) {
+            TORCH_CHECK(a_scale->scalar_type() == torch::kFloat32 && a_scale->size(0) == rows && a_scale->size(1) == K / 128, "a_scale: fp32 [rows, K/128]");
+            g.a_scale = a_scale->data_ptr<float>();
+            g.a_scale_s0 = a_scale->stride(0);
+            g.a_scale_s1 = a_scale->stride(1);
+        } else {
+            TORCH_CHECK(gather && a_scale_offset >= K && a_scale_offset % 4 == 0 && a_scale_offset + (K / 128) * 4 <= g.a_pitch,
+                        "FP8 operands need a_scale, or gathered records with the scales at a_scale_offset");
+            g.a_scale_off = (int)a_scale_offset;
+        }
+    }
+    g.out = quantize_out ? nullptr : reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
+    if (quantize_out) {
+        g.out_q = static_cast<unsigned char*>(out_q.data_ptr());
+        g.out_q_scale = out_q_scale.data_ptr<float>();
+        g.oqs0 = out_q_scale.stride(0);
+        g.oqs1 = out_q_scale.stride(1);
+    }
+    g.ldc = (int)ldc;
+    g.swiglu = swiglu ? 1 : 0;
+    g.row_scale = row_scale.has_value() ? row_scale->data_ptr<float>() : nullptr;
+    if (rows == 0) return result;
+    g.error = checked_gemm_error_word(w.get_device());
+    int sms = 0;
+    rt_check(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, w.get_device()), "device attribute");
+    const int grid = ctas > 0 ? (int)ctas : sms;
+    const CUtensorMap map_w = make_tile_map(w.data_ptr(), E * N, K, elem, 256);
+    const CUtensorMap map_a = gather ? map_w : make_tile_map(a.data_ptr(), rows, K, elem, 128);
+    FusedReceive fr{};
+    rt_check(launch_expert_gemm(map_a, map_w, g, gather, fr, grid, at::cuda::getCurrentCUDAStream().stream()), "expert_gemm launch");
+    return result;
+}
+
 // (e4m3 [rows, K], fp32 scales [rows, K/128]) from bf16 rows; `limit` (optional int32 device
 // tensor, e.g. recv_count_psum[-1:]) marks the first row that need not be quantised.
-py::tuple quantize_rows_fp8(const torch::Tensor& x, const c10::optional<torch::Tensor>& limit) {
+py::tuple quantize_rows_fp8(const torch::Tensor& x, const c10::optional<torch::Tensor>& limit, bool pow2) {
     TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.scalar_type() == torch::kBFloat16 && x.is_contiguous(), "x: contiguous CUDA bf16 [rows, K]");
     const int64_t rows = x.size(0), K = x.size(1);
     TORCH_CHECK(K % 128 == 0, "K must be a multiple of 128");
@@ -634,7 +894,7 @@ py::tuple quantize_rows_fp8(const torch::Tensor& x, const c10::optional<torch::T
     }
     int sms = 0;
     rt_check(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, x.get_device()), "device attribute");
-    rt_check(launch_quantize_rows(x.data_ptr(), q.data_ptr(), scale.data_ptr<float>(), (int)rows, (int)K, scale.stride(0), scale.stride(1), lim,
+    rt_check(launch_quantize_rows(x.data_ptr(), q.data_ptr(), scale.data_ptr<float>(), (int)rows, (int)K, scale.stride(0), scale.stride(1), lim, pow2,
                                   sms * 8, at::cuda::getCurrentCUDAStream().stream()),
              "quantize launch");
     return py::make_tuple(q, scale);
@@ -702,8 +962,18 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     });
     m.def("grouped_gemm", &afdep::grouped_gemm, py::arg("a"), py::arg("w"), py::arg("ends"), py::arg("alignment"),
           py::arg("swiglu") = false, py::arg("row_scale") = py::none(), py::arg("a_scale") = py::none(),
-          py::arg("w_scale") = py::none(), py::arg("out") = py::none(), py::arg("ctas") = 0, py::arg("quantize_out") = false, py::arg("swapped") = false);
-    m.def("quantize_rows_fp8", &afdep::quantize_rows_fp8, py::arg("x"), py::arg("limit") = py::none());
+          py::arg("w_scale") = py::none(), py::arg("out") = py::none(), py::arg("ctas") = 0, py::arg("quantize_out") = false);
+    m.def("expert_gemm", &afdep::expert_gemm, py::arg("a"), py::arg("w"), py::arg("ends"), py::arg("alignment"), py::arg("swiglu") = false,
+          py::arg("row_scale") = py::none(), py::arg("a_scale") = py::none(), py::arg("w_scale") = py::none(), py::arg("out") = py::none(),
+          py::arg("ctas") = 0, py::arg("quantize_out") = false, py::arg("row_index") = py::none(), py::arg("a_scale_offset") = -1);
+    // True (and cleared) if an expert GEMM on this device gave up on a bounded wait since the last check.
+    m.def("gemm_check", [](int device) {
+        const afdep::GemmErrorWord w = afdep::gemm_error_word(device);
+        if (w.host == nullptr || *w.host == 0) return false;
+        *w.host = 0;
+        return true;
+    });
+    m.def("quantize_rows_fp8", &afdep::quantize_rows_fp8, py::arg("x"), py::arg("limit") = py::none(), py::arg("pow2") = false);
     m.def("route_layout", &afdep::route_layout, py::arg("ids"), py::arg("num_experts"), py::arg("ffn_ranks"));
     py::class_<NativeBuffer>(m, "NativeBuffer")
         .def(py::init<int, int, int, int, int, int, int, bool, int, int, int, int, double, int64_t, const std::string&, bool>(),
@@ -724,6 +994,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("source_collect", &NativeBuffer::source_collect)
         .def("worker_receive", &NativeBuffer::worker_receive)
         .def("worker_reply", &NativeBuffer::worker_reply)
+        .def("worker_mlp_fused", &NativeBuffer::worker_mlp_fused)
         .def("status", &NativeBuffer::status)
         .def("status_code", &NativeBuffer::status_code)
         .def("clear_status", &NativeBuffer::clear_status)
@@ -739,6 +1010,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("p2p_send", &NativeBuffer::p2p_send)
         .def("p2p_recv", &NativeBuffer::p2p_recv)
         .def("fetch_rows", &NativeBuffer::fetch_rows)
+        .def("set_dispatch_ctas", &NativeBuffer::set_dispatch_ctas)
+        .def("poison_payload", &NativeBuffer::poison_payload)
         .def("launches", &NativeBuffer::launches)
         .def("resolved_num_sms", &NativeBuffer::resolved_num_sms)
         .def("device_sms", &NativeBuffer::device_sms)

@@ -1,4 +1,4 @@
-"""Grouped expert GEMM on tcgen05 tensor cores, and the plain-torch reference it is tested against.
+"""Grouped expert GEMMs on tcgen05 tensor cores, and the plain-torch reference they are tested against.
 
 ``grouped_gemm(a, w, ends, alignment, ...)`` multiplies the expert-major rows returned by
 ``worker_receive`` with one weight matrix per local expert:
@@ -21,22 +21,40 @@ GATE_UP_BLOCK = 32   # rows of gate, then rows of up, alternating in the fused g
 
 
 def grouped_gemm(a, w, ends, alignment: int, *, swiglu: bool = False, row_scale=None, a_scale=None, w_scale=None, out=None, ctas: int = 0,
-                 quantize_out: bool = False, tile: str = "wide"):
-    """``quantize_out=True`` (FP8 operands with ``swiglu``, wide tile): the epilogue quantises the
-    SwiGLU output and returns ``(e4m3 [rows, N/2], fp32 scales [rows, N/256])`` instead of BF16, in
-    the per-row, per-128-column format the FP8 GEMM takes as its ``a`` operand.
+                 quantize_out: bool = False):
+    """The promoting kernel: BF16, or e4m3 with arbitrary fp32 block scales (every 128-deep K
+    block is scaled in registers on its way out of tensor memory).
 
-    ``tile``: ``"wide"`` (128 rows x 256 columns per tile, the default) or ``"swapped"`` (128
-    weight rows x 64 tokens: the weights are the MMA's M operand).  Measured on a B200 with 16
-    rows per expert, 64 experts, FP8: wide 0.336 ms / swapped 0.423 ms for 4096 x 7168 weights,
-    0.195 / 0.264 ms for 7168 x 2048 -- the wide tile already streams the weights at 4.8-5.6 TB/s
-    there, so the swapped tile is an alternative kept for narrower batches, not the default."""
+    ``quantize_out=True`` (FP8 operands with ``swiglu``): the epilogue quantises the SwiGLU output
+    and returns ``(e4m3 [rows, N/2], fp32 scales [rows, N/256])`` instead of BF16, in the per-row,
+    per-128-column format the FP8 GEMM takes as its ``a`` operand."""
     from .._native import load_native
 
-    if tile not in ("wide", "swapped"):
-        raise ValueError("tile must be 'wide' or 'swapped'")
-    return load_native().grouped_gemm(a, w, ends, int(alignment), bool(swiglu), row_scale, a_scale, w_scale, out, int(ctas), bool(quantize_out),
-                                      tile == "swapped")
+    return load_native().grouped_gemm(a, w, ends, int(alignment), bool(swiglu), row_scale, a_scale, w_scale, out, int(ctas), bool(quantize_out))
+
+
+def expert_gemm(a, w, ends, alignment: int, *, swiglu: bool = False, row_scale=None, a_scale=None, w_scale=None, out=None, ctas: int = 0,
+                quantize_out: bool = False, row_index=None, a_scale_offset: int = -1):
+    """The self-feeding kernel: BF16, or e4m3 whose fp32 block scales are **powers of two**
+    (``quantize_*(..., pow2=True)``).  The tensor core applies the scales itself
+    (``tcgen05.mma ... block_scale``), so the whole K extent accumulates in tensor memory.
+
+    ``row_index`` (int32 ``[rows]``) switches to the gathered form: row ``r`` of the product's row
+    space is read from ``a[row_index[r]]`` (negative: a row of zeros), ``a`` being any contiguous
+    2-D tensor whose rows start with the K operand elements -- for instance the wire records of an
+    exchange, viewed as ``uint8 [records, record_bytes]`` with each record's fp32 scales at byte
+    offset ``a_scale_offset``.  ``quantize_out`` returns e4m3 with power-of-two scales."""
+    from .._native import load_native
+
+    return load_native().expert_gemm(a, w, ends, int(alignment), bool(swiglu), row_scale, a_scale, w_scale, out, int(ctas), bool(quantize_out),
+                                     row_index, int(a_scale_offset))
+
+
+def gemm_check(device: int | None = None) -> bool:
+    """True (once) if an expert GEMM on ``device`` abandoned a bounded wait since the last check."""
+    from .._native import load_native
+
+    return bool(load_native().gemm_check(torch.cuda.current_device() if device is None else int(device)))
 
 
 def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
@@ -78,26 +96,36 @@ def reference_grouped_gemm(a, w, ends, alignment, *, swiglu=False, row_scale=Non
     return out
 
 
-def quantize_rows_fp8_cuda(x: torch.Tensor, limit: torch.Tensor | None = None):
+def pow2_ceil(scale: torch.Tensor) -> torch.Tensor:
+    """Positive fp32 values rounded up to powers of two (exact as exponent bytes)."""
+    return torch.exp2(torch.ceil(torch.log2(scale.double()))).float()
+
+
+def quantize_rows_fp8_cuda(x: torch.Tensor, limit: torch.Tensor | None = None, pow2: bool = False):
     """The same quantisation as ``quantize_rows_fp8`` in one CUDA kernel (bf16 input on the GPU).
     ``limit``: optional int32 device tensor; rows at or beyond ``limit[0]`` are left unwritten."""
     from .._native import load_native
 
-    return load_native().quantize_rows_fp8(x, limit)
+    return load_native().quantize_rows_fp8(x, limit, bool(pow2))
 
 
-def quantize_rows_fp8(x: torch.Tensor):
-    """e4m3 rows with one fp32 scale per row and 128 columns (amax / 448)."""
+def quantize_rows_fp8(x: torch.Tensor, pow2: bool = False):
+    """e4m3 rows with one fp32 scale per row and 128 columns (amax / 448, optionally rounded up
+    to a power of two)."""
     rows, K = x.shape
     g = x.float().view(rows, K // 128, 128)
     scale = g.abs().amax(dim=2).clamp_min(1e-12) / 448.0
+    if pow2:
+        scale = pow2_ceil(scale)
     return (g / scale[:, :, None]).reshape(rows, K).to(torch.float8_e4m3fn), scale
 
 
-def quantize_weight_blocks_fp8(w: torch.Tensor):
+def quantize_weight_blocks_fp8(w: torch.Tensor, pow2: bool = False):
     """e4m3 weights with one fp32 scale per 128 x 128 block: ([E, N, K] e4m3, [E, N/128, K/128])."""
     E, N, K = w.shape
     g = w.float().view(E, N // 128, 128, K // 128, 128)
     scale = g.abs().amax(dim=(2, 4)).clamp_min(1e-12) / 448.0
+    if pow2:
+        scale = pow2_ceil(scale)
     q = (g / scale[:, :, None, :, None]).reshape(E, N, K).to(torch.float8_e4m3fn)
     return q, scale.contiguous()

@@ -36,7 +36,12 @@ class NativeTransport:
         self.float32, self.bfloat16 = torch.float32, torch.bfloat16
         self._failed: str | None = None
         self._loopback = bool(options.get("loopback", False))
-        self._col_major_scale = options.get("recv_scale_layout", "row_major") == "col_major_tma"
+        # recv_scale comes back column-major with a 4-aligned leading dimension, as the reference
+        # always returns it (csrc/elastic/buffer.hpp:1067-1078); "row_major" is the option.
+        layout = options.get("recv_scale_layout", "col_major_tma")
+        if layout not in ("col_major_tma", "row_major"):
+            raise ValueError("recv_scale_layout must be 'col_major_tma' or 'row_major'")
+        self._col_major_scale = layout == "col_major_tma"
 
         timeout_s = float(config.gpu_timeout_s)
         if os.environ.get("AFDEP_TIMEOUT_MS"):
@@ -251,6 +256,21 @@ class NativeTransport:
             lambda: self._on_comm_stream(
                 lambda: self._nb.worker_receive(rows, read_host_counts, float(self.config.cpu_timeout_s), self._col_major_scale)
             ),
+        )
+
+    def worker_mlp_fused(self, weights, *, bucket: int):
+        """Layout pass, gathered gate|up GEMM, down GEMM and reply of one exchange; returns
+        ``(psum, recv_weights, recv_src, rows)``."""
+        fp8 = self.config.is_fp8
+        if fp8 and (weights.mode != "fp8" or weights.w_down_scale is None or getattr(weights, "scale_format", "fp32") != "pow2"):
+            raise ValueError("the fused expert path takes FP8 payloads only with FP8 experts whose block scales are powers of two")
+        if not fp8 and weights.mode != "bf16":
+            raise ValueError("the fused expert path takes BF16 payloads only with BF16 experts")
+        rows = self.config.receive_rows(bucket)
+        tensors = (weights.w_gate_up, weights.w_gate_up_scale, weights.w_down, weights.w_down_scale)
+        return self._ranged(
+            "worker_mlp_fused",
+            lambda: self._on_comm_stream(lambda: self._nb.worker_mlp_fused(tensors[0], tensors[1], tensors[2], tensors[3], rows), *tensors),
         )
 
     def worker_reply(self, rows) -> None:

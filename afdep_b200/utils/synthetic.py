@@ -39,16 +39,24 @@ def zipf_probs(num_experts: int, s: float, generator: torch.Generator) -> torch.
     return probs.float()
 
 
-def quantize_fp8(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
-    """e4m3 rows with one fp32 scale per 128 channels (amax / 448)."""
+def pow2_ceil(scale: torch.Tensor) -> torch.Tensor:
+    """Every positive fp32 value rounded up to a power of two (exact as an exponent byte)."""
+    return torch.exp2(torch.ceil(torch.log2(scale.double()))).float()
+
+
+def quantize_fp8(x: torch.Tensor, pow2: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
+    """e4m3 rows with one fp32 scale per 128 channels (amax / 448; ``pow2`` rounds the scale up
+    to a power of two, the form the hardware block-scaled expert GEMM takes)."""
     rows, hidden = x.shape
     g = x.float().view(rows, hidden // 128, 128)
     scale = g.abs().amax(dim=2).clamp_min(1e-12) / 448.0
+    if pow2:
+        scale = pow2_ceil(scale)
     q = (g / scale[:, :, None]).reshape(rows, hidden).to(torch.float8_e4m3fn)
     return q, scale
 
 
-def random_batch(config: Config, tokens: int, seed: int, *, zipf_s: float | None = None, skip_fraction: float = 0.0):
+def random_batch(config: Config, tokens: int, seed: int, *, zipf_s: float | None = None, skip_fraction: float = 0.0, pow2_scales: bool = False):
     """(x, ids, weights, x_scale) on the CPU for one attention rank."""
     gen = torch.Generator().manual_seed(seed)
     x = torch.randn((tokens, config.hidden_size), generator=gen)
@@ -63,7 +71,7 @@ def random_batch(config: Config, tokens: int, seed: int, *, zipf_s: float | None
         ids = torch.where(drop, torch.full_like(ids, -1), ids)
         weights = torch.where(drop, torch.zeros_like(weights), weights)
     if config.is_fp8:
-        q, scale = quantize_fp8(x)
+        q, scale = quantize_fp8(x, pow2_scales)
         return q, ids, weights, scale
     return x.to(torch.bfloat16), ids, weights, None
 

@@ -50,7 +50,6 @@ def parse_args():
     p.add_argument("--impl", choices=("ours", "nccl", "reference"), default="ours")
     p.add_argument("--config", choices=tuple(CONFIGS), default="weak")
     p.add_argument("--expert-weights", choices=("fp8", "bf16"), default="fp8", help="config 5: storage of the expert weights")
-    p.add_argument("--gemm-tile", choices=("wide", "swapped"), default="wide", help="config 5: tile shape of the expert GEMMs")
     p.add_argument("--expert-down", choices=("fp8", "bf16"), default=None, help="config 5: storage of the down projection (default: like --expert-weights)")
     p.add_argument("--tokens", type=int, default=0, help="override tokens per attention rank")
     p.add_argument("--num-sms", type=int, default=0)
@@ -289,8 +288,6 @@ def main() -> None:
         phase_log[name].append((a, b))
         return out
 
-    gemm_tile = args.gemm_tile
-
     def step(copy_inputs: bool, record: bool = False):
         """One exchange in dependency order; returns the collected output on attention ranks."""
         result = None
@@ -308,7 +305,7 @@ def main() -> None:
                 if "weights" in s:
                     from afdep_b200.models.moe_layer import run_experts
 
-                    rows = mark("experts", lambda: run_experts(rec, s["weights"], cfg.expert_alignment, tile=gemm_tile), record)
+                    rows = mark("experts", lambda: run_experts(rec, s["weights"], cfg.expert_alignment), record)
                 else:
                     rows = rec.recv_x if not cfg.is_fp8 else s["rows"]
                 s["psum"] = rec.recv_count_psum
@@ -464,7 +461,7 @@ def main() -> None:
             else None
         ),
         "expert_weights": (
-            {"gate_up": args.expert_weights, "down": args.expert_down or args.expert_weights, "gemm_tile": args.gemm_tile}
+            {"gate_up": args.expert_weights, "down": args.expert_down or args.expert_weights}
             if "intermediate" in spec
             else None
         ),

@@ -1,6 +1,11 @@
 """Micro-benchmark of the tcgen05 grouped expert GEMM against its roofline.
 
     python bench_gemm.py [--rows-per-expert 256] [--experts 64] [--n 4096] [--k 7168] [--dtype fp8|bf16] [--swiglu]
+                         [--kernel promoting|selffeeding] [--gather]
+
+``--kernel promoting`` is `grouped_gemm` (fp32 block scales promoted through registers),
+``--kernel selffeeding`` is `expert_gemm` (power-of-two block scales applied by the tensor core;
+``--gather`` reads the rows of A by index out of a shuffled matrix of records).
 
 Times the kernel with CUDA events (warm-up, L2 flushed between iterations) and reports
 achieved TFLOP/s next to the measured cuBLAS BF16 peak of `MEASURED_PEAKS.json` (FP8 is
@@ -30,7 +35,8 @@ def main() -> None:
     p.add_argument("--iters", type=int, default=10)
     p.add_argument("--ctas", type=int, default=0)
     p.add_argument("--skip-cublas", action="store_true")
-    p.add_argument("--tile", choices=("wide", "swapped"), default="wide", help="128 x 256 tiles, or 128 weight rows x 64 tokens")
+    p.add_argument("--kernel", choices=("promoting", "selffeeding"), default="selffeeding")
+    p.add_argument("--gather", action="store_true", help="self-feeding kernel: gather A rows by index from shuffled records")
     a = p.parse_args()
     torch.cuda.set_device(0)
     E, N, K, R = a.experts, a.n, a.k, a.rows_per_expert
@@ -42,11 +48,12 @@ def main() -> None:
         w[e] = (torch.randn(N, K, device="cuda") * 0.02).to(torch.bfloat16)
     kw = {}
     if a.dtype == "fp8":
-        xa, a_scale = gg.quantize_rows_fp8(x)
+        pow2 = a.kernel == "selffeeding"
+        xa, a_scale = gg.quantize_rows_fp8(x, pow2)
         wq = torch.empty(E, N, K, device="cuda", dtype=torch.float8_e4m3fn)
         ws = torch.empty(E, N // 128, K // 128, device="cuda")
         for e in range(E):
-            q, s = gg.quantize_weight_blocks_fp8(w[e : e + 1].float())
+            q, s = gg.quantize_weight_blocks_fp8(w[e : e + 1].float(), pow2)
             wq[e], ws[e] = q[0], s[0]
         wa, kw = wq, dict(a_scale=a_scale, w_scale=ws)
     else:
@@ -68,7 +75,29 @@ def main() -> None:
                 ts.append(e0.elapsed_time(e1))
         return sum(ts) / len(ts), min(ts)
 
-    mean_ms, best_ms = timed(lambda: gg.grouped_gemm(xa, wa, ends, 128, swiglu=a.swiglu, out=out, ctas=a.ctas, tile=a.tile, **kw))
+    if a.kernel == "promoting":
+        assert not a.gather, "--gather belongs to the self-feeding kernel"
+        run = lambda: gg.grouped_gemm(xa, wa, ends, 128, swiglu=a.swiglu, out=out, ctas=a.ctas, **kw)      # noqa: E731
+    elif a.gather:
+        perm = torch.randperm(rows, device="cuda")
+        index = torch.empty(rows, dtype=torch.int32, device="cuda")
+        index[perm] = torch.arange(rows, dtype=torch.int32, device="cuda")           # row r lives in record index[r]
+        if a.dtype == "fp8":
+            rec_bytes = (K + (K // 128) * 4 + 127) // 128 * 128
+            records = torch.zeros(rows, rec_bytes, dtype=torch.uint8, device="cuda")
+            records[index.long(), :K] = xa.view(torch.uint8)
+            records[index.long(), K : K + (K // 128) * 4] = kw["a_scale"].contiguous().view(torch.uint8).view(rows, -1)
+            run = lambda: gg.expert_gemm(records, wa, ends, 128, swiglu=a.swiglu, out=out, ctas=a.ctas, w_scale=kw["w_scale"],      # noqa: E731
+                                         row_index=index, a_scale_offset=K)
+        else:
+            records = torch.zeros(rows, K + 64, dtype=torch.bfloat16, device="cuda")
+            records[index.long(), :K] = xa
+            run = lambda: gg.expert_gemm(records, wa, ends, 128, swiglu=a.swiglu, out=out, ctas=a.ctas, row_index=index)             # noqa: E731
+    else:
+        run = lambda: gg.expert_gemm(xa, wa, ends, 128, swiglu=a.swiglu, out=out, ctas=a.ctas, **kw)        # noqa: E731
+    mean_ms, best_ms = timed(run)
+    torch.cuda.synchronize()
+    assert not gg.gemm_check(), "a kernel gave up on a bounded wait"
     peaks = {}
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -76,7 +105,7 @@ def main() -> None:
     bf16_peak = peaks.get("bf16_tflops", 1590.0)
     peak = bf16_peak * (2.0 if a.dtype == "fp8" else 1.0)
     res = {
-        "kernel": "grouped_gemm", "tile": a.tile, "dtype": a.dtype, "swiglu": a.swiglu, "experts": E, "rows_per_expert": R, "N": N, "K": K,
+        "kernel": "grouped_gemm" if a.kernel == "promoting" else "expert_gemm", "gather": a.gather, "dtype": a.dtype, "swiglu": a.swiglu, "experts": E, "rows_per_expert": R, "N": N, "K": K,
         "ms_mean": round(mean_ms, 4), "ms_best": round(best_ms, 4),
         "tflops_mean": round(flops / mean_ms / 1e9, 1), "tflops_best": round(flops / best_ms / 1e9, 1),
         "peak_tflops": peak, "peak_source": "measured cuBLAS bf16" + (" x2 for fp8" if a.dtype == "fp8" else "") if peaks else "fallback",

@@ -114,7 +114,7 @@ def test_random_routes_large_hidden(payload):
 
 def test_strided_scales_and_column_major_output():
     cfg = Config(16, 512, 8, 2, 2, 2, expert_alignment=4, payload="fp8")
-    world = make_world(cfg, recv_scale_layout="col_major_tma")
+    world = make_world(cfg)           # column-major receive scales are the default
     try:
         batches = []
         for a in range(2):
@@ -233,6 +233,130 @@ def test_cuda_graph_replay_with_changed_inputs():
                     assert torch.equal(outs[a].cpu().float(), expect)
         for b in world.buffers:
             b.check()
+    finally:
+        world.close()
+
+
+def _negate_(x):
+    """Flip the sign of every element in place (BF16, or e4m3 through its sign bit)."""
+    if x.dtype == torch.bfloat16:
+        x.neg_()
+    else:
+        x.view(torch.uint8).bitwise_xor_(0x80)
+
+
+@pytest.mark.parametrize("payload", ["bf16", "fp8"])
+def test_deep_graph_of_alternating_sign_exchanges(payload):
+    """24 complete exchanges per graph, the input's sign flipped in place before each one, so two
+    consecutive exchanges never carry the same payload; 14 replays with routes, token counts and
+    values changed in place between them (the depth of the reference's own graph check,
+    tests/gpu/deepep.py:205-238).  Between replays every payload region of the heap and the
+    tensors of the previous replay are overwritten with NaN bit patterns: a row read from a stale
+    slot would surface as NaN."""
+    cfg = Config(16, 512, 8, 2, 2, 2, expert_alignment=4, payload=payload)
+    world = make_world(cfg)
+    try:
+        n, steps, replays = 16, 24, 14
+        first = [to_dev(synthetic.exact_batch(cfg, n, a, 0)) for a in range(2)]
+        static = [[t.clone() if t is not None else None for t in b] for b in first]
+        leftovers = []
+
+        def expert(i, rec):
+            rows = oracle.synthetic_expert_rows(cfg, i, rec.recv_x, rec.recv_scale, rec.recv_topk_weights, rec.recv_count_psum)
+            leftovers.append(rec.recv_x)
+            return rows
+
+        stream = torch.cuda.Stream()
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            for _ in range(2):
+                world.exchange(static, expert)
+        torch.cuda.synchronize()
+        leftovers.clear()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            captured = []
+            for _ in range(steps):
+                for b in static:
+                    _negate_(b[0])
+                captured.append(world.exchange(static, expert)[0])
+        torch.cuda.synchronize()
+        routings = ["mixed", "mixed", "skew", "skip", "mixed"]
+        for epoch in range(1, replays + 1):
+            routing = routings[epoch % len(routings)]
+            new = [synthetic.exact_batch(cfg, n, a, epoch, active=n - (epoch + 3 * a) % 5, routing=routing) for a in range(2)]
+            for s, b in zip(static, new):
+                for dst, src in zip(s, b):
+                    if dst is not None:
+                        dst.copy_(src)
+            for buf in world.buffers:
+                buf._t._nb.poison_payload()
+            for t in leftovers:                      # receive tensors of the captured exchanges (graph-private memory)
+                t.view(torch.uint8).fill_(0xFF)
+            for outs in captured:
+                for o in outs:
+                    o.view(torch.int16).fill_(-1)    # 0xFFFF: NaN in BF16
+            graph.replay()
+            torch.cuda.synchronize()
+            for a in range(2):
+                expect = oracle.expected_combine(cfg, oracle.SourceBatch(*new[a])).float()
+                for i, outs in enumerate(captured):
+                    sign = -1.0 if i % 2 == 0 else 1.0      # the i-th exchange sees the input negated i + 1 times
+                    got = outs[a].cpu().float()
+                    assert not torch.isnan(got).any(), f"replay {epoch}, exchange {i}: stale data"
+                    assert torch.equal(got, sign * expect), f"replay {epoch}, exchange {i}, attention rank {a}"
+        for b in world.buffers:
+            b.check()
+        assert world.buffers[0].stats()["launches"] > 0
+    finally:
+        world.close()
+
+
+def test_eager_exchanges_survive_nan_poison_between_them():
+    """Eager mode: heap payload regions and the previous exchange's receive and reply tensors are
+    filled with NaN bit patterns before every exchange; results must still equal the oracle."""
+    cfg = Config(64, 1024, 16, 4, 2, 2, expert_alignment=8, payload="fp8")
+    world = make_world(cfg)
+    try:
+        stale = []
+        for epoch in range(4):
+            for buf in world.buffers:
+                buf._t._nb.poison_payload()
+            for t in stale:
+                t.view(torch.uint8).fill_(0xFF)
+            batches = [synthetic.exact_batch(cfg, 64 - 5 * epoch, a, epoch) for a in range(2)]
+            outs, received = run_and_check(world, cfg, batches)
+            stale = [r.recv_x for r in received] + [r.recv_topk_weights for r in received] + list(outs)
+    finally:
+        world.close()
+
+
+def test_dispatch_grid_is_co_resident_or_refused():
+    """The distributed-layout dispatch is a cooperative launch: with a compute kernel hogging the
+    SMs on another stream it still completes (it starts once the whole grid fits), and a grid the
+    GPU can never hold at once is refused on the host with an error, not left to time out."""
+    cfg = Config(4096, 1024, 16, 4, 1, 1, expert_alignment=8)     # enough tokens for more CTAs than the GPU has SMs
+    world = make_world(cfg)
+    try:
+        batches = [synthetic.random_batch(cfg, 4096, seed=3)]
+        side = torch.cuda.Stream()
+        a = torch.randn(8192, 8192, device="cuda", dtype=torch.bfloat16)
+        with torch.cuda.stream(side):
+            for _ in range(6):
+                a @ a                                 # a few milliseconds of GEMMs that fill every SM
+        run_and_check(world, cfg, batches, exact=False)
+        side.synchronize()
+        sms = torch.cuda.get_device_properties(0).multi_processor_count
+        att = world.attention[0]
+        att._t._nb.set_dispatch_ctas(min(160, sms + 12))
+        if sms + 12 <= 160:
+            x, ids, w, _ = to_dev(batches[0])
+            with pytest.raises(RuntimeError, match="dispatch launch"):
+                att.source_dispatch(x, ids, w, None, bucket=4096)
+            att.transport._pending = None
+            torch.cuda.synchronize()
+            att._t._nb.set_dispatch_ctas(sms)
+            run_and_check(world, cfg, batches, exact=False)      # the Buffer is still usable
     finally:
         world.close()
 

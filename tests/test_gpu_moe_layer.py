@@ -18,32 +18,65 @@ def _dequant_blocks(w, scale):
     return (w.float().view(E, N // 128, 128, K // 128, 128) * scale.view(E, N // 128, 1, K // 128, 1)).reshape(E, N, K)
 
 
-@pytest.mark.parametrize("tile", ["wide", "swapped"])
-@pytest.mark.parametrize("payload,mode,down", [("bf16", "bf16", "bf16"), ("fp8", "fp8", "fp8"), ("bf16", "fp8", "fp8"), ("fp8", "fp8", "bf16")])
-def test_moe_layer_matches_dense_reference(payload, mode, down, tile):
+CASES = [
+    # payload, expert storage, down projection, FP8 scale format, fused receive -> experts -> reply
+    ("bf16", "bf16", "bf16", "fp32", False),
+    ("fp8", "fp8", "fp8", "fp32", False),
+    ("bf16", "fp8", "fp8", "fp32", False),
+    ("fp8", "fp8", "bf16", "fp32", False),
+    ("fp8", "fp8", "fp8", "pow2", False),
+    ("bf16", "fp8", "fp8", "pow2", False),
+    ("bf16", "bf16", "bf16", "fp32", True),
+    ("fp8", "fp8", "fp8", "pow2", True),
+]
+
+
+@pytest.mark.parametrize("payload,mode,down,scale_format,fused", CASES)
+def test_moe_layer_matches_dense_reference(payload, mode, down, scale_format, fused):
     from afdep_b200.parallel.loopback import LoopbackWorld
 
     hidden, inter, experts, top_k, ffn, attn, tokens = 512, 256, 8, 2, 2, 2, 96
+    pow2 = scale_format == "pow2"
     cfg = Config(tokens, hidden, experts, top_k, ffn, attn, expert_alignment=128, payload=payload)
     world = LoopbackWorld(cfg, gpu_timeout_s=5.0)
     try:
         el = cfg.experts_per_rank
-        weights = [ExpertWeights.random(el, hidden, inter, mode=mode, down=down, seed=10 + f) for f in range(ffn)]
-        batches = [synthetic.random_batch(cfg, tokens - 7 * a, seed=a) for a in range(attn)]
+        weights = [ExpertWeights.random(el, hidden, inter, mode=mode, down=down, seed=10 + f, scale_format=scale_format) for f in range(ffn)]
+        batches = [synthetic.random_batch(cfg, tokens - 7 * a, seed=a, pow2_scales=pow2) for a in range(attn)]
         dev = [tuple(None if t is None else t.cuda() for t in b) for b in batches]
-        kept = {}
 
         def expert(i, rec):
-            kept[i] = rec
-            return run_experts(rec, weights[i], cfg.expert_alignment, tile=tile)
+            return run_experts(rec, weights[i], cfg.expert_alignment)
 
         outs, received = world.exchange(dev, expert)
         torch.cuda.synchronize()
+        if fused:
+            # the same exchange again, this time with the experts reading the wire records directly
+            unfused_outs = outs
+            unfused_rows = [run_experts(rec, weights[i], cfg.expert_alignment) for i, rec in enumerate(received)]
+            for buf, (x, ids, w, scale) in zip(world.attention, dev):
+                buf.source_dispatch(x, ids, w, scale, bucket=tokens)
+            served = [buf.worker_serve_fused(weights[i], bucket=tokens) for i, buf in enumerate(world.ffn)]
+            outs = [buf.source_collect() for buf in world.attention]
+            torch.cuda.synchronize()
+            for i, ((res, rows), rec) in enumerate(zip(served, received)):
+                assert res.recv_x is None and torch.equal(res.recv_count_psum, rec.recv_count_psum)
+                ends = rec.recv_count_psum.cpu().tolist()
+                start = 0
+                for end in ends:
+                    start = (start + 127) // 128 * 128
+                    assert torch.equal(res.recv_topk_weights[start:end], rec.recv_topk_weights[start:end])
+                    assert torch.equal(res.handle.recv_src_metadata[start:end], rec.handle.recv_src_metadata[start:end])
+                    torch.testing.assert_close(rows[start:end].float(), unfused_rows[i][start:end].float(), rtol=2e-2, atol=1e-3)
+                    start = end
+            for o, u in zip(outs, unfused_outs):
+                torch.testing.assert_close(o.float(), u.float(), rtol=2e-2, atol=2e-3)
         for b in world.buffers:
             b.check()
+        assert not gg.gemm_check()
         # the kernels' rows against the fp32 reference of the same MLP on the same received rows
         for i, rec in enumerate(received):
-            got = run_experts(rec, weights[i], cfg.expert_alignment, tile=tile).float()
+            got = run_experts(rec, weights[i], cfg.expert_alignment).float()
             want = reference_experts(rec, weights[i], cfg.expert_alignment).float()
             ends = rec.recv_count_psum.cpu().tolist()
             start = 0
@@ -70,7 +103,7 @@ def test_moe_layer_matches_dense_reference(payload, mode, down, tile):
                     y = y.view(y.shape[0], -1, 2, 32)
                     h = (torch.nn.functional.silu(y[:, :, 0]) * y[:, :, 1]).reshape(y.shape[0], -1)
                     if wt.w_down_scale is not None:      # the kernels quantise the SwiGLU output for an FP8 down projection
-                        hq, hs = gg.quantize_rows_fp8(h)
+                        hq, hs = gg.quantize_rows_fp8(h, pow2)
                         h = (hq.float().view(h.shape[0], -1, 128) * hs[:, :, None]).reshape(h.shape)
                     else:
                         h = h.to(torch.bfloat16).float()

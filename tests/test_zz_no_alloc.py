@@ -66,6 +66,11 @@ def test_no_alloc_entry_point_matches_route_layout_twice():
         torch.cuda.synchronize()
         for name, g, w in zip(("route_e", "route_pos", "tok_slot", "counts"), got, want):
             assert torch.equal(g, w), f"call {call}: {name} differs from route_layout"
+        route_e, _, tok_slot, counts = got
+        # the two outcomes that no return code reports: the illegal token comes back blanked,
+        # and counts of -1 would mean the launch gave up on its wait between CTAs
+        assert bool((route_e[3] == -1).all()) and bool((tok_slot[3] == -1).all())
+        assert bool((counts >= 0).all())
 
 
 def test_no_alloc_entry_point_rejects_oversized_requests():
