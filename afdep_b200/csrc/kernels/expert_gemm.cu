@@ -151,6 +151,9 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         }
         ctrl->tile_prefix[p.experts] = run;
     }
+    // The row-maximum mailboxes are matched by tile number, starting at 1: clear what an earlier
+    // kernel on this SM left in shared memory, or a stale entry could pass for this launch's.
+    for (int i = tid; i < 2 * 2 * BM; i += blockDim.x) (&ctrl->amax_x[0][0][0])[i] = 0ull;
     if (warp == 1) {
         tc::tmem_alloc(&ctrl->tmem_base, kTmemCols);
         tc::tmem_relinquish();
@@ -271,7 +274,6 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                         break;
                     }
                     tc::fence_after_sync();
-                    if (kGather) ptx::fence_proxy_async_smem();     // gathered rows were written by ordinary copies
                     const unsigned char* sa = smem + stage * kStageBytes;
                     const unsigned char* sb = sa + BM * 128;
                     const uint32_t sfa = tmem + (uint32_t)(kSfBase + slot * kSfSlotCols);
@@ -376,51 +378,66 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 ++tcount;
             }
             const int row_limit = min(p.ends[e], p.rows);
+            // Scales of one group (four K blocks): four rows per lane for A, two 128-column blocks for W.
+            // They are fetched one group ahead, so their latency never holds up the row gathering.
+            float sa[4][4], sb[2][4];
+            auto fetch_scales = [&](int kb0) {
+                const int kgroups = p.K / 128;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int r = 32 * j + lane;
+                    if (kGather && p.a_scale == nullptr) {
+                        float4 v = make_float4(1.f, 1.f, 1.f, 1.f);
+                        if (rec_s[j] >= 0)
+                            v = __ldcg(reinterpret_cast<const float4*>(p.a_rows + (size_t)rec_s[j] * p.a_pitch + p.a_scale_off) + (kb0 >> 2));
+                        sa[j][0] = v.x;
+                        sa[j][1] = v.y;
+                        sa[j][2] = v.z;
+                        sa[j][3] = v.w;
+                    } else {
+#pragma unroll
+                        for (int b = 0; b < 4; ++b)
+                            sa[j][b] = (kb0 + b < num_kb && row0 + r < row_limit)
+                                           ? __ldg(p.a_scale + (size_t)(row0 + r) * p.a_scale_s0 + (size_t)(kb0 + b) * p.a_scale_s1)
+                                           : 1.f;
+                    }
+                }
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int nb = col0 / 128 + h;
+#pragma unroll
+                    for (int b = 0; b < 4; ++b)
+                        sb[h][b] = (kb0 + b < num_kb && nb * 128 < p.N) ? __ldg(p.w_scale + ((size_t)e * (p.N / 128) + nb) * kgroups + kb0 + b) : 1.f;
+                }
+            };
+            if (kMx) fetch_scales(0);
             bool ok = true;
             for (int kb = 0; kb < num_kb; ++kb) {
                 if (kMx && (kb & 3) == 0) {
                     // exponent bytes of K blocks kb .. kb+3: A's rows (4 columns), W's columns (8 columns)
                     const unsigned slot = group % kSfSlots;
+                    uint32_t wa[4], wb[8];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint32_t word = 0;
+#pragma unroll
+                        for (int b = 0; b < 4; ++b) word |= ((kb + b < num_kb) ? tc::ue8m0_of_pow2(sa[j][b]) : 127u) << (8 * b);
+                        wa[j] = word;
+                    }
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        uint32_t word = 0;
+#pragma unroll
+                        for (int b = 0; b < 4; ++b) word |= ((kb + b < num_kb) ? tc::ue8m0_of_pow2(sb[h][b]) : 127u) << (8 * b);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) wb[4 * h + j] = word;
+                    }
+                    if (kb + 4 < num_kb) fetch_scales(kb + 4);      // in flight while the next four stages are fed
                     if (!wait_bar_warp(&ctrl->sf_empty[slot], ((group / kSfSlots) & 1u) ^ 1u, failed, p.budget)) {
                         ok = false;
                         break;
                     }
                     tc::fence_after_sync();
-                    uint32_t wa[4];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int r = 32 * j + lane;
-                        uint32_t word = 0;
-#pragma unroll
-                        for (int b = 0; b < 4; ++b) {
-                            float s = 1.f;
-                            if (kb + b < num_kb) {
-                                if (kGather && p.a_scale == nullptr) {
-                                    if (rec_s[j] >= 0)
-                                        s = __ldcg(reinterpret_cast<const float*>(p.a_rows + (size_t)rec_s[j] * p.a_pitch + p.a_scale_off) + kb + b);
-                                } else if (row0 + r < row_limit) {
-                                    s = __ldg(p.a_scale + (size_t)(row0 + r) * p.a_scale_s0 + (size_t)(kb + b) * p.a_scale_s1);
-                                }
-                            }
-                            word |= tc::ue8m0_of_pow2(s) << (8 * b);
-                        }
-                        wa[j] = word;
-                    }
-                    uint32_t wb[8];
-                    const int kgroups = p.K / 128;
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        const int nb = col0 / 128 + h;
-                        uint32_t word = 0;
-#pragma unroll
-                        for (int b = 0; b < 4; ++b) {
-                            float s = 1.f;
-                            if (kb + b < num_kb && nb * 128 < p.N) s = __ldg(p.w_scale + ((size_t)e * (p.N / 128) + nb) * kgroups + kb + b);
-                            word |= tc::ue8m0_of_pow2(s) << (8 * b);
-                        }
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) wb[4 * h + j] = word;
-                    }
                     const uint32_t dst = tmem + lane_base + (uint32_t)(kSfBase + slot * kSfSlotCols);
                     tc::tmem_st4(dst, wa[0], wa[1], wa[2], wa[3]);
                     tc::tmem_st8(dst + 4, wb);

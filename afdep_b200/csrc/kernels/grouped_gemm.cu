@@ -113,6 +113,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
         ctrl->tile_prefix[p.experts] = run;
     }
+    // The row-maximum mailboxes are matched by tile number, starting at 1: clear what an earlier
+    // kernel on this SM left in shared memory, or a stale entry could pass for this launch's.
+    for (int i = tid; i < 2 * 2 * BM; i += blockDim.x) (&ctrl->amax_x[0][0][0])[i] = 0ull;
     if (warp == 1) {
         tc::tmem_alloc(&ctrl->tmem_base, kTmemCols);
         tc::tmem_relinquish();

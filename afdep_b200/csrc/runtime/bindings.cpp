@@ -17,6 +17,7 @@
 #include <chrono>
 #include <cstdlib>
 #include <memory>
+#include <mutex>
 #include <thread>
 
 #include "afdep/aux_api.h"
@@ -79,6 +80,21 @@ CUtensorMap make_tile_map(const void* base, int64_t rows, int64_t cols, int elem
 
 }  // namespace
 
+// SM clock in kHz, asked once per device: this attribute is a live driver query (milliseconds),
+// not a cached property, so it must stay off the launch path.
+int device_khz(int device) {
+    static std::mutex mu;
+    static int cache[64] = {};
+    std::lock_guard<std::mutex> lock(mu);
+    if (device < 0 || device >= 64) device = 0;
+    if (cache[device] == 0) {
+        int khz = 0;
+        rt_check(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, device), "device attribute");
+        cache[device] = khz > 0 ? khz : 1000000;
+    }
+    return cache[device];
+}
+
 // The device's GEMM error word, after raising for any failure an earlier launch left in it.  A
 // kernel whose bounded wait ran out sets the word and returns with its output incomplete; the
 // next GEMM call on that device (or gemm_check) reports it.
@@ -96,8 +112,9 @@ class NativeBuffer {
 public:
     NativeBuffer(int rank, int ffn, int attn, int hidden, int top_k, int num_experts, int capacity, bool fp8,
                  int alignment, int num_sms, int collect_sms, int ffn_sms, double gpu_timeout_s,
-                 int64_t aux_bytes, const std::string& heap_mode, bool bounds_check)
-        : rank_(rank), num_sms_(num_sms), collect_sms_(collect_sms), ffn_sms_(ffn_sms) {
+                 int64_t aux_bytes, const std::string& heap_mode, bool bounds_check, int p2p_inflight)
+        : rank_(rank), num_sms_(num_sms), collect_sms_(collect_sms), ffn_sms_(ffn_sms), p2p_inflight_(p2p_inflight) {
+        TORCH_CHECK(p2p_inflight >= 1 && p2p_inflight <= 64, "p2p_inflight must be between 1 and 64");
         TORCH_CHECK(ffn + attn <= kMaxRanks, "the native transport supports at most ", kMaxRanks, " ranks");
         TORCH_CHECK(num_experts <= kMaxExperts && num_experts / ffn <= kMaxExpertsLocal, "too many experts");
         TORCH_CHECK(top_k <= kMaxTopK, "top_k too large");
@@ -119,6 +136,7 @@ public:
         if (collect_sms_ <= 0 || collect_sms_ > sms) collect_sms_ = sms;
         if (ffn_sms_ <= 0 || ffn_sms_ > sms) ffn_sms_ = sms;
         rt_check(configure_kernels(max_smem_), "cudaFuncSetAttribute");
+        rt_check(configure_aux(), "cudaFuncSetAttribute");
 
         // status block and host-count mailbox in mapped pinned memory
         rt_check(cudaHostAlloc(&host_block_, kHostBlockBytes, cudaHostAllocMapped), "cudaHostAlloc");
@@ -492,7 +510,11 @@ public:
 
     // ---- secondary primitives on the auxiliary region ----------------------------------------
     int64_t aux_data_bytes() const { return geo_.aux_bytes > (size_t)kAuxSignalBytes ? (int64_t)(geo_.aux_bytes - kAuxSignalBytes) : 0; }
-    int64_t aux_slot_bytes() const { return aux_data_bytes() / geo_.world / 16 * 16; }
+    // Largest all-gather contribution (two slot sets, by gather parity) and largest message
+    // (a ring of p2p_inflight slots per source rank).
+    int64_t aux_slot_bytes() const { return aux_data_bytes() / (2 * geo_.world) / 16 * 16; }
+    int64_t p2p_slot_bytes() const { return aux_data_bytes() / ((int64_t)geo_.world * p2p_inflight_) / 16 * 16; }
+    int p2p_inflight() const { return p2p_inflight_; }
 
     // View of this rank's auxiliary data area as bytes (peers write into it).
     torch::Tensor aux_view() {
@@ -502,7 +524,7 @@ public:
     }
     void allgather_push(const torch::Tensor& t) {
         live();
-        const size_t bytes = check_aux_tensor(t);
+        const size_t bytes = check_aux_tensor(t, aux_slot_bytes());
         rt_check(launch_allgather_push(ctx_, aux_seq(), t.data_ptr(), bytes, (size_t)aux_slot_bytes(), aux_ctas(bytes), stream()), "all-gather launch");
         ++launches_;
     }
@@ -513,7 +535,7 @@ public:
     // re-read from the device (one stream synchronisation) before every use.
     void allgather_push_copy(const torch::Tensor& t) {
         live();
-        const size_t bytes = check_aux_tensor(t);
+        const size_t bytes = check_aux_tensor(t, aux_slot_bytes());
         cudaStream_t s = stream();
         cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
         rt_check(cudaStreamIsCapturing(s, &cap), "cudaStreamIsCapturing");
@@ -523,35 +545,49 @@ public:
             rt_check(cudaMemcpy(&gathers_done_, aux_seq().gather, sizeof(unsigned), cudaMemcpyDeviceToHost), "cudaMemcpy");
         }
         const size_t slot = (size_t)aux_slot_bytes();
+        const size_t set = (size_t)((gathers_done_ + 1u) & 1u) * geo_.world;       // slot set of this gather's parity
         std::vector<StreamWrite32> flags;
         for (int p = 0; p < geo_.world; ++p) {
             char* aux = ctx_.peer[p] + geo_.aux_off;
-            rt_check(cudaMemcpyAsync(aux + kAuxSignalBytes + (size_t)rank_ * slot, t.data_ptr(), bytes, cudaMemcpyDeviceToDevice, s),
+            rt_check(cudaMemcpyAsync(aux + kAuxSignalBytes + (set + (size_t)rank_) * slot, t.data_ptr(), bytes, cudaMemcpyDeviceToDevice, s),
                      "all-gather peer copy");
             flags.push_back({aux + sizeof(uint32_t) * (size_t)rank_, gathers_done_ + 1u});
         }
         stream_write32_batch(s, flags);
     }
-    void allgather_wait() {
+    // Waits for every rank's contribution and returns a copy of the gathered bytes
+    // [world, nbytes]: the heap slots are free for the gather after next as soon as this returns.
+    torch::Tensor allgather_wait(int64_t nbytes) {
         live();
+        TORCH_CHECK(nbytes >= 0 && nbytes <= aux_slot_bytes(), "gathered size exceeds the slot");
+        cudaStream_t s = stream();
         cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-        rt_check(cudaStreamIsCapturing(stream(), &cap), "cudaStreamIsCapturing");
-        if (cap == cudaStreamCaptureStatusNone) ++gathers_done_; else gather_in_graph_ = true;
-        rt_check(launch_allgather_wait(ctx_, aux_seq(), stream()), "all-gather wait launch");
-        ++launches_;
+        rt_check(cudaStreamIsCapturing(s, &cap), "cudaStreamIsCapturing");
+        auto out = torch::empty({geo_.world, nbytes}, torch::TensorOptions().dtype(torch::kUInt8).device(torch::kCUDA, device_));
+        if (cap != cudaStreamCaptureStatusNone)
+            gather_in_graph_ = true;       // replays advance the device count behind the host's back
+        else
+            ++gathers_done_;
+        // The copy-out reads the gather's parity from the device count, so it is right in graph replays too.
+        rt_check(launch_allgather_wait(ctx_, aux_seq(), s), "all-gather wait launch");
+        rt_check(launch_allgather_copy_out(ctx_, aux_seq(), out.data_ptr(), (size_t)nbytes, (size_t)aux_slot_bytes(), s), "all-gather copy launch");
+        launches_ += 2;
+        return out;
     }
     void p2p_send(const torch::Tensor& t, int dst) {
         live();
         check_peer(dst);
-        const size_t bytes = check_aux_tensor(t);
-        rt_check(launch_p2p_send(ctx_, aux_seq(), dst, t.data_ptr(), bytes, (size_t)aux_slot_bytes(), aux_ctas(bytes), stream()), "send launch");
+        const size_t bytes = check_aux_tensor(t, p2p_slot_bytes());
+        rt_check(launch_p2p_send(ctx_, aux_seq(), dst, t.data_ptr(), bytes, (size_t)p2p_slot_bytes(), p2p_inflight_, aux_ctas(bytes), stream()),
+                 "send launch");
         ++launches_;
     }
     void p2p_recv(torch::Tensor& t, int src) {
         live();
         check_peer(src);
-        const size_t bytes = check_aux_tensor(t);
-        rt_check(launch_p2p_recv(ctx_, aux_seq(), src, t.data_ptr(), bytes, (size_t)aux_slot_bytes(), aux_ctas(bytes), stream()), "recv launch");
+        const size_t bytes = check_aux_tensor(t, p2p_slot_bytes());
+        rt_check(launch_p2p_recv(ctx_, aux_seq(), src, t.data_ptr(), bytes, (size_t)p2p_slot_bytes(), p2p_inflight_, aux_ctas(bytes), stream()),
+                 "recv launch");
         ++launches_;
     }
     torch::Tensor fetch_rows(const torch::Tensor& idx, int64_t rows_per_rank, int64_t row_bytes) {
@@ -631,15 +667,16 @@ private:
         q.ticket = reinterpret_cast<unsigned*>(fl + 56);
         return q;
     }
-    size_t check_aux_tensor(const torch::Tensor& t) const {
+    size_t check_aux_tensor(const torch::Tensor& t, int64_t slot) const {
         TORCH_CHECK(t.is_cuda() && t.is_contiguous(), "tensor must be a contiguous CUDA tensor");
         const size_t bytes = (size_t)t.numel() * t.element_size();
         TORCH_CHECK(bytes % 16 == 0 && reinterpret_cast<uintptr_t>(t.data_ptr()) % 16 == 0, "tensor must be 16-byte aligned and sized");
-        TORCH_CHECK((int64_t)bytes <= aux_slot_bytes(), "tensor larger than the per-peer slot of the auxiliary region (raise aux_bytes)");
+        TORCH_CHECK((int64_t)bytes <= slot, "tensor larger than its slot of the auxiliary region (raise aux_bytes)");
         return bytes;
     }
+    // One CTA (one copy engine) per 128 KB, at most the communication SM budget.
     int aux_ctas(size_t bytes) const {
-        const int want = (int)((bytes + 65535) / 65536);
+        const int want = (int)((bytes + 131071) / 131072);
         return want < 1 ? 1 : (want > num_sms_ ? num_sms_ : want);
     }
 
@@ -658,7 +695,7 @@ private:
     }
 
     int rank_, role_rank_ = 0, device_ = 0, device_sms_ = 0, max_smem_ = 0;
-    int num_sms_, collect_sms_, ffn_sms_;
+    int num_sms_, collect_sms_, ffn_sms_, p2p_inflight_;
     bool is_ffn_ = false, destroyed_ = false, failed_ = false;
     Geometry geo_{};
     RankCtx ctx_{};
@@ -692,8 +729,7 @@ py::tuple route_layout(const torch::Tensor& ids, int64_t num_experts, int64_t ff
     auto route_pos = torch::empty({T, K}, i32);
     auto tok_slot = torch::empty({T, ffn_ranks}, i32);
     auto counts = torch::empty({ffn_ranks + num_experts}, i32);
-    int khz = 0;
-    rt_check(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, ids.get_device()), "device attribute");
+    const int khz = device_khz(ids.get_device());
     rt_check(launch_route_layout(reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()), (int)T, (int)K,
                                  (int)num_experts, (int)ffn_ranks, scratch.data_ptr(), route_e.data_ptr<int>(),
                                  route_pos.data_ptr<int>(), tok_slot.data_ptr<int>(), counts.data_ptr<int>(),
@@ -832,9 +868,7 @@ py::object expert_gemm(const torch::Tensor& a, const torch::Tensor& w, const tor
     g.alignment = (int)alignment;
     g.ends = ends.data_ptr<int>();
     g.mx = fp8 ? 1 : 0;
-    int khz = 0;
-    rt_check(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, w.get_device()), "device attribute");
-    g.budget = (long long)khz * 1000ll * 10ll;
+    g.budget = (long long)device_khz(w.get_device()) * 1000ll * 10ll;
     g.a_scale_off = -1;
     if (gather) {
         g.a_rows = static_cast<const unsigned char*>(a.data_ptr());
@@ -851,8 +885,8 @@ py::object expert_gemm(const torch::Tensor& a, const torch::Tensor& w, const tor
             g.a_scale_s0 = a_scale->stride(0);
             g.a_scale_s1 = a_scale->stride(1);
         } else {
-            TORCH_CHECK(gather && a_scale_offset >= K && a_scale_offset % 4 == 0 && a_scale_offset + (K / 128) * 4 <= g.a_pitch,
-                        "FP8 operands need a_scale, or gathered records with the scales at a_scale_offset");
+            TORCH_CHECK(gather && a_scale_offset >= K && a_scale_offset % 16 == 0 && a_scale_offset + ((K / 128 + 3) / 4) * 16 <= g.a_pitch,
+                        "FP8 operands need a_scale, or gathered records with the scales (padded to whole 16-byte groups) at a 16-byte aligned a_scale_offset");
             g.a_scale_off = (int)a_scale_offset;
         }
     }
@@ -976,10 +1010,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("quantize_rows_fp8", &afdep::quantize_rows_fp8, py::arg("x"), py::arg("limit") = py::none(), py::arg("pow2") = false);
     m.def("route_layout", &afdep::route_layout, py::arg("ids"), py::arg("num_experts"), py::arg("ffn_ranks"));
     py::class_<NativeBuffer>(m, "NativeBuffer")
-        .def(py::init<int, int, int, int, int, int, int, bool, int, int, int, int, double, int64_t, const std::string&, bool>(),
+        .def(py::init<int, int, int, int, int, int, int, bool, int, int, int, int, double, int64_t, const std::string&, bool, int>(),
              py::arg("rank"), py::arg("ffn"), py::arg("attn"), py::arg("hidden"), py::arg("top_k"), py::arg("num_experts"),
              py::arg("capacity"), py::arg("fp8"), py::arg("alignment"), py::arg("num_sms"), py::arg("collect_sms"),
-             py::arg("ffn_sms"), py::arg("gpu_timeout_s"), py::arg("aux_bytes"), py::arg("heap_mode"), py::arg("bounds_check"))
+             py::arg("ffn_sms"), py::arg("gpu_timeout_s"), py::arg("aux_bytes"), py::arg("heap_mode"), py::arg("bounds_check"), py::arg("p2p_inflight") = 4)
         .def("heap_bytes", &NativeBuffer::heap_bytes)
         .def("mapped_bytes", &NativeBuffer::mapped_bytes)
         .def("local_ptr", &NativeBuffer::local_ptr)
@@ -1002,6 +1036,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("trace", &NativeBuffer::trace)
         .def("aux_data_bytes", &NativeBuffer::aux_data_bytes)
         .def("aux_slot_bytes", &NativeBuffer::aux_slot_bytes)
+        .def("p2p_slot_bytes", &NativeBuffer::p2p_slot_bytes)
+        .def("p2p_inflight", &NativeBuffer::p2p_inflight)
         .def("aux_view", &NativeBuffer::aux_view)
         .def("allgather_push", &NativeBuffer::allgather_push)
         .def("enable_expert_stats", &NativeBuffer::enable_expert_stats)

@@ -64,14 +64,14 @@ class ExpertWeights:
         gen = torch.Generator(device=device).manual_seed(seed)
         E, I, H = num_local_experts, intermediate, hidden
         gate_up = torch.empty((E, 2 * I, H), device=device, dtype=torch.bfloat16)
-        down = torch.empty((E, H, I), device=device, dtype=torch.bfloat16)
+        down_w = torch.empty((E, H, I), device=device, dtype=torch.bfloat16)
         for e in range(E):       # expert by expert: the fp32 staging stays small
             wg = torch.randn((I, H), generator=gen, device=device) * std
             wu = torch.randn((I, H), generator=gen, device=device) * std
             gate_up[e] = gg.interleave_gate_up(wg[None], wu[None])[0].to(torch.bfloat16)
-            down[e] = (torch.randn((H, I), generator=gen, device=device) * std).to(torch.bfloat16)
+            down_w[e] = (torch.randn((H, I), generator=gen, device=device) * std).to(torch.bfloat16)
         if mode == "bf16":
-            return ExpertWeights(gate_up, None, down, I, mode)
+            return ExpertWeights(gate_up, None, down_w, I, mode)
         q = torch.empty((E, 2 * I, H), device=device, dtype=torch.float8_e4m3fn)
         scale = torch.empty((E, 2 * I // 128, H // 128), device=device, dtype=torch.float32)
         down_q = torch.empty((E, H, I), device=device, dtype=torch.float8_e4m3fn) if down == "fp8" else None
@@ -79,15 +79,15 @@ class ExpertWeights:
         for e in range(E):
             qe, se = gg.quantize_weight_blocks_fp8(gate_up[e : e + 1].float(), pow2)
             q[e], scale[e] = qe[0], se[0]
-            de, ds = gg.quantize_weight_blocks_fp8(down[e : e + 1].float(), pow2)
+            de, ds = gg.quantize_weight_blocks_fp8(down_w[e : e + 1].float(), pow2)
             if down == "fp8":
                 down_q[e], down_scale[e] = de[0], ds[0]
             else:
                 blocks = de.float().view(1, H // 128, 128, I // 128, 128) * ds.view(1, H // 128, 1, I // 128, 1)
-                down[e] = blocks.reshape(H, I).to(torch.bfloat16)      # e4m3-rounded values, BF16 storage
+                down_w[e] = blocks.reshape(H, I).to(torch.bfloat16)      # e4m3-rounded values, BF16 storage
         if down == "fp8":
             return ExpertWeights(q, scale, down_q, I, mode, down_scale, scale_format)
-        return ExpertWeights(q, scale, down, I, mode)
+        return ExpertWeights(q, scale, down_w, I, mode)
 
 
 def run_experts(received: ReceiveResult, weights: ExpertWeights, alignment: int, *, scratch: dict | None = None) -> torch.Tensor:

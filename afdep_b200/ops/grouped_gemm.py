@@ -97,8 +97,11 @@ def reference_grouped_gemm(a, w, ends, alignment, *, swiglu=False, row_scale=Non
 
 
 def pow2_ceil(scale: torch.Tensor) -> torch.Tensor:
-    """Positive fp32 values rounded up to powers of two (exact as exponent bytes)."""
-    return torch.exp2(torch.ceil(torch.log2(scale.double()))).float()
+    """Positive fp32 values rounded up to powers of two (exact: mantissa and exponent are split,
+    never a logarithm)."""
+    mant, exp = torch.frexp(scale.float())               # scale = mant * 2^exp, mant in [0.5, 1)
+    exp = exp - (mant == 0.5).to(exp.dtype)              # already a power of two: keep it
+    return torch.ldexp(torch.ones_like(mant), exp)
 
 
 def quantize_rows_fp8_cuda(x: torch.Tensor, limit: torch.Tensor | None = None, pow2: bool = False):
@@ -114,7 +117,7 @@ def quantize_rows_fp8(x: torch.Tensor, pow2: bool = False):
     to a power of two)."""
     rows, K = x.shape
     g = x.float().view(rows, K // 128, 128)
-    scale = g.abs().amax(dim=2).clamp_min(1e-12) / 448.0
+    scale = (g.abs().amax(dim=2).double().clamp_min(1e-12) / 448.0).float()     # true division (a scalar divisor may be turned into a reciprocal)
     if pow2:
         scale = pow2_ceil(scale)
     return (g / scale[:, :, None]).reshape(rows, K).to(torch.float8_e4m3fn), scale
@@ -124,7 +127,7 @@ def quantize_weight_blocks_fp8(w: torch.Tensor, pow2: bool = False):
     """e4m3 weights with one fp32 scale per 128 x 128 block: ([E, N, K] e4m3, [E, N/128, K/128])."""
     E, N, K = w.shape
     g = w.float().view(E, N // 128, 128, K // 128, 128)
-    scale = g.abs().amax(dim=(2, 4)).clamp_min(1e-12) / 448.0
+    scale = (g.abs().amax(dim=(2, 4)).double().clamp_min(1e-12) / 448.0).float()
     if pow2:
         scale = pow2_ceil(scale)
     q = (g / scale[:, :, None, :, None]).reshape(E, N, K).to(torch.float8_e4m3fn)

@@ -79,6 +79,7 @@ class NativeTransport:
             aux_bytes=int(options.get("aux_bytes", 0)),
             heap_mode=mode,
             bounds_check=bounds,
+            p2p_inflight=int(options.get("p2p_inflight", 4)),
         )
         self.num_buffer_bytes = int(self._nb.heap_bytes())
         self.num_sms = num_sms

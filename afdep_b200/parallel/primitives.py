@@ -2,7 +2,10 @@
 with credits, and remote row fetch.  NVLink only.
 
 They live in the heap's auxiliary region, whose size is chosen when the Buffer is built
-(``Buffer(..., aux_bytes=...)``); each rank's data area holds one slot per peer.  The
+(``Buffer(..., aux_bytes=..., p2p_inflight=4)``).  The three primitives share that data area,
+one at a time (separate phases with ``barrier()``): an all-gather uses two sets of one slot per
+rank, send/recv a ring of ``p2p_inflight`` message slots per source rank, the row fetch this
+rank's shard of the table.  The
 reference inherits comparable calls from its vendored transport (pipeline send/recv, an
 in-session all-gather and an embedding-row fetch, csrc/elastic/buffer.hpp:201-474) without
 exposing them in its role API; here they are a thin, explicit layer next to the role API.
@@ -24,18 +27,32 @@ class HeapPrimitives:
         self._nb = buffer._t._nb
         self.world_size = buffer.config.world_size
         self.rank = buffer.rank
+        self._side = None
         if self._nb.aux_slot_bytes() <= 0:
             raise ValueError("build the Buffer with aux_bytes > 0 to use heap primitives")
 
     @property
     def slot_bytes(self) -> int:
-        """Largest message / gathered tensor per rank."""
+        """Largest tensor a rank can contribute to an all-gather."""
         return int(self._nb.aux_slot_bytes())
+
+    @property
+    def message_bytes(self) -> int:
+        """Largest send/recv message."""
+        return int(self._nb.p2p_slot_bytes())
+
+    @property
+    def inflight(self) -> int:
+        """Messages a sender can have on their way to one peer before it waits for that peer."""
+        return int(self._nb.p2p_inflight())
 
     # ---- all-gather ---------------------------------------------------------------------
     def all_gather_start(self, tensor: torch.Tensor, *, engine: str = "sm"):
         """Push ``tensor`` into every peer's slot for this rank.  Returns a handle whose
-        ``wait()`` yields the ``[world_size, *tensor.shape]`` view of the gathered data.
+        ``wait()`` yields the gathered data ``[world_size, *tensor.shape]`` as a tensor of its own
+        (copied out of the heap on the current stream, so gathers may follow one another without
+        a barrier: the slots alternate between two sets and a set is reused only after every
+        rank has copied its previous contents out).
 
         ``engine="sm"`` copies with a kernel (graph-capturable).  ``engine="copy"`` uses one
         copy-engine transfer per peer and a batched stream memory operation for the flags, so
@@ -54,7 +71,8 @@ class HeapPrimitives:
 
     # ---- neighbour send / recv -------------------------------------------------------------
     def send(self, tensor: torch.Tensor, dst: int) -> None:
-        """One message to ``dst``; waits (on the device) until ``dst`` consumed the previous one."""
+        """One message to ``dst``.  Up to ``inflight`` messages may be on their way; the kernel of
+        message ``n`` waits (bounded, on the device) until ``dst`` has consumed message ``n - inflight``."""
         self._nb.p2p_send(tensor, int(dst))
 
     def recv(self, out: torch.Tensor, src: int) -> torch.Tensor:
@@ -75,6 +93,22 @@ class HeapPrimitives:
         raw = self._nb.fetch_rows(idx, int(rows_per_rank), int(row_bytes))
         return raw.view(dtype).view(idx.numel(), row_elems)
 
+    def fetch_rows_start(self, idx: torch.Tensor, rows_per_rank: int, row_elems: int, dtype: torch.dtype) -> "_FetchHandle":
+        """Issue the same fetch on a side stream and return at once; ``handle.wait()`` makes the
+        current stream wait for it and hands over the rows.  Work queued on the current stream
+        between the two calls overlaps the transfer (the reference splits its fetch into an
+        issue and a wait kernel for the same purpose, impls/engram_fetch.cuh:11-97)."""
+        if self._side is None:
+            self._side = torch.cuda.Stream(device=idx.device)
+        current = torch.cuda.current_stream(idx.device)
+        self._side.wait_stream(current)
+        with torch.cuda.stream(self._side):
+            rows = self.fetch_rows(idx, rows_per_rank, row_elems, dtype)
+            done = torch.cuda.Event()
+            done.record(self._side)
+        idx.record_stream(self._side)
+        return _FetchHandle(rows, done)
+
     def barrier(self) -> None:
         """Device-side barrier over all ranks on the current stream."""
         self._nb.barrier()
@@ -86,8 +120,16 @@ class _GatherHandle:
 
     def wait(self) -> torch.Tensor:
         o = self._owner
-        o._nb.allgather_wait()
-        view = o._nb.aux_view()
-        slot = o.slot_bytes
-        rows = view[: o.world_size * slot].view(o.world_size, slot)[:, : self._nbytes]
-        return rows.view(self._dtype).view(o.world_size, *self._shape) if rows.is_contiguous() else rows.contiguous().view(self._dtype).view(o.world_size, *self._shape)
+        raw = o._nb.allgather_wait(int(self._nbytes))          # uint8 [world, nbytes], a copy
+        return raw.view(self._dtype).view(o.world_size, *self._shape)
+
+
+class _FetchHandle:
+    def __init__(self, rows: torch.Tensor, done) -> None:
+        self._rows, self._done = rows, done
+
+    def wait(self) -> torch.Tensor:
+        current = torch.cuda.current_stream(self._rows.device)
+        current.wait_event(self._done)
+        self._rows.record_stream(current)
+        return self._rows

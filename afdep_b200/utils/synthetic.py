@@ -40,8 +40,11 @@ def zipf_probs(num_experts: int, s: float, generator: torch.Generator) -> torch.
 
 
 def pow2_ceil(scale: torch.Tensor) -> torch.Tensor:
-    """Every positive fp32 value rounded up to a power of two (exact as an exponent byte)."""
-    return torch.exp2(torch.ceil(torch.log2(scale.double()))).float()
+    """Positive fp32 values rounded up to powers of two (exact: mantissa and exponent are split,
+    never a logarithm)."""
+    mant, exp = torch.frexp(scale.float())               # scale = mant * 2^exp, mant in [0.5, 1)
+    exp = exp - (mant == 0.5).to(exp.dtype)              # already a power of two: keep it
+    return torch.ldexp(torch.ones_like(mant), exp)
 
 
 def quantize_fp8(x: torch.Tensor, pow2: bool = False) -> tuple[torch.Tensor, torch.Tensor]:
@@ -49,7 +52,7 @@ def quantize_fp8(x: torch.Tensor, pow2: bool = False) -> tuple[torch.Tensor, tor
     to a power of two, the form the hardware block-scaled expert GEMM takes)."""
     rows, hidden = x.shape
     g = x.float().view(rows, hidden // 128, 128)
-    scale = g.abs().amax(dim=2).clamp_min(1e-12) / 448.0
+    scale = (g.abs().amax(dim=2).double().clamp_min(1e-12) / 448.0).float()
     if pow2:
         scale = pow2_ceil(scale)
     q = (g / scale[:, :, None]).reshape(rows, hidden).to(torch.float8_e4m3fn)

@@ -1,21 +1,28 @@
 """Headline benchmark: dispatch + combine of one AFD expert-parallel exchange.
 
-    python bench.py --gpus N --steps K --warmup W [--impl ours|nccl|reference] [--config weak|2|3|4]
+    python bench.py --gpus N --steps K --warmup W [--impl ours|nccl|reference] [--config weak|2|3|4|5]
 
 N = 1 runs one attention and one FFN rank colocated on a single GPU (all ranks in this
 process); N >= 2 expects one process per GPU (torchrun) and splits the ranks N/2 FFN + N/2
 attention (6 attention + 2 FFN for ``--config 4``).  A step is one complete exchange through
 the public role API: ``source_dispatch`` -> ``worker_receive`` -> ``worker_reply`` ->
 ``source_collect``.  The FFN "expert" is the identity on a preallocated BF16 tensor, so the
-timed region holds the library's four kernels and nothing else.
+timed region holds the library's four kernels and nothing else; ``--config 5`` puts SwiGLU
+experts on tcgen05 in between (fused with the receive unless ``--unfused``).
 
-Every step is bracketed by CUDA events on the launching stream after a device-side barrier
-across ranks (outside the events); L2 is flushed between steps; the reported time is the
-maximum over ranks.  ``value`` is the job's aggregate wire throughput: bytes that cross NVLink
-in both directions (one record per token and destination FFN rank out, one BF16 row back)
-divided by the step time.  The ``e2e`` entry repeats the measurement with, inside the timed
-region, the host->device copy of the step's inputs from pinned memory and a device->host read
-of a checksum of the result.
+Timing.  Every step is bracketed by CUDA events on the launching stream after a device-side
+barrier across ranks (outside the events); L2 is flushed between steps.  K steps form a round;
+rounds are repeated until the timed region spans at least 0.3 s, the round whose time is the
+median supplies ``ms_per_step`` (maximum over ranks per round) and the spread is reported as
+p10/p90.  ``value`` is the job's aggregate wire throughput: bytes that cross NVLink in both
+directions (one record per token and destination FFN rank out, one BF16 row back) divided by
+the step time; ``us_per_exchange`` and ``per_rank_GBs`` are the per-rank figures.  ``phases``
+are kernel durations read from device time stamps of one traced graph replay.  The ``e2e``
+entry repeats the measurement with, inside the timed region and every step, the host->device
+copy of the step's inputs from pinned memory and a device->host read of a checksum of the
+result: ``serial`` issues the copy on the compute stream, the headline e2e ``value`` stages
+step n+1's copy on a second stream while step n runs.  With ``--gpus 8`` the line also carries
+sub-results for the 8-GPU configurations 3, 4 and 5 under ``extra``.
 """
 
 from __future__ import annotations
@@ -41,6 +48,12 @@ CONFIGS = {
     "5": dict(hidden=7168, experts_per_ffn=64, top_k=8, tokens=2048, payload="fp8", zipf=None, intermediate=2048),
 }
 
+# NVLink rate per direction per GPU: nominal, and what a bulk-copy kernel of this library reaches
+# between two B200s of this pool (bench_nvlink.py; summary in profiles/nvlink_p2p_rate.md).
+NVLINK_NOMINAL_GBS = 900.0
+NVLINK_MEASURED_GBS = 770.0
+MIN_TIMED_SECONDS = 0.3
+
 
 def parse_args():
     p = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
@@ -51,6 +64,10 @@ def parse_args():
     p.add_argument("--config", choices=tuple(CONFIGS), default="weak")
     p.add_argument("--expert-weights", choices=("fp8", "bf16"), default="fp8", help="config 5: storage of the expert weights")
     p.add_argument("--expert-down", choices=("fp8", "bf16"), default=None, help="config 5: storage of the down projection (default: like --expert-weights)")
+    p.add_argument("--expert-scales", choices=("pow2", "fp32"), default="pow2",
+                   help="config 5, FP8: block scales rounded up to powers of two and applied by the tensor core (default), or arbitrary fp32 scales promoted through registers")
+    p.add_argument("--unfused", action="store_true", help="config 5: worker_receive -> experts -> worker_reply as separate calls")
+    p.add_argument("--no-extra", action="store_true", help="--gpus 8: skip the sub-results for configs 3, 4 and 5")
     p.add_argument("--tokens", type=int, default=0, help="override tokens per attention rank")
     p.add_argument("--num-sms", type=int, default=0)
     p.add_argument("--graph", action="store_true", help="(default for --impl ours) replay each timed step from a CUDA graph")
@@ -165,82 +182,114 @@ def reference_arm(args) -> None:
         print(json.dumps({"impl": "reference", "unavailable": reason}))
 
 
-def main() -> None:
-    args = parse_args()
-    if args.impl == "reference":
-        reference_arm(args)
-        return
+def percentile(values, q):
+    v = sorted(values)
+    if not v:
+        return None
+    pos = (len(v) - 1) * q
+    lo = int(pos)
+    hi = min(lo + 1, len(v) - 1)
+    return v[lo] + (v[hi] - v[lo]) * (pos - lo)
 
+
+class Env:
+    """Process-wide state shared by the configurations measured in one invocation."""
+
+    def __init__(self, args) -> None:
+        import torch
+
+        self.args, self.n = args, args.gpus
+        self.multi = self.n > 1
+        if self.multi:
+            import datetime
+
+            import torch.distributed as dist
+
+            self.rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+            assert world == self.n, "launch with torchrun --nproc-per-node equal to --gpus"
+            self.local = int(os.environ.get("LOCAL_RANK", self.rank))
+            torch.cuda.set_device(self.local)
+            dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=600))
+        else:
+            self.rank, self.local = 0, 0
+            torch.cuda.set_device(0)
+        self.dev = torch.device("cuda", self.local)
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=self.dev)
+
+    def gather(self, obj):
+        if not self.multi:
+            return [obj]
+        import torch.distributed as dist
+
+        out = [None] * self.n
+        dist.all_gather_object(out, obj)
+        return out
+
+    def host_barrier(self):
+        if self.multi:
+            import torch.distributed as dist
+
+            dist.barrier()
+
+
+def run_config(env: Env, name: str, *, steps: int, warmup: int, tokens: int = 0, with_e2e: bool = True, trace_print: bool = False,
+               sampler: ClockSampler | None = None) -> dict:
+    """Build the Buffers of one configuration, measure it, close them; returns the result record."""
     import torch
-    import torch.distributed as dist
 
     from afdep_b200 import Buffer, Config
     from afdep_b200.utils import synthetic
 
-    n = args.gpus
-    spec = dict(CONFIGS[args.config])
-    if args.tokens:
-        spec["tokens"] = args.tokens
-    ffn, attn = topology(n, args.config)
+    args, n, multi, dev = env.args, env.n, env.multi, env.dev
+    spec = dict(CONFIGS[name])
+    if tokens:
+        spec["tokens"] = tokens
+    ffn, attn = topology(n, name)
     T = spec["tokens"]
-    cfg = Config(
-        T,
-        spec["hidden"],
-        spec["experts_per_ffn"] * ffn,
-        spec["top_k"],
-        ffn,
-        attn,
-        payload=spec["payload"],
-        num_sms=args.num_sms,
-        gpu_timeout_s=20,
-        cpu_timeout_s=60,
-    )
-    multi = n > 1
+    experts_on = "intermediate" in spec
+    pow2 = experts_on and args.expert_weights == "fp8" and (args.expert_down or "fp8") == "fp8" and args.expert_scales == "pow2"
+    fused = experts_on and not args.unfused and args.impl == "ours" and (pow2 or args.expert_weights == "bf16")
+    payload = spec["payload"]
+    if experts_on and args.expert_weights == "bf16":
+        payload = "bf16"
+    cfg = Config(T, spec["hidden"], spec["experts_per_ffn"] * ffn, spec["top_k"], ffn, attn, payload=payload, num_sms=args.num_sms,
+                 gpu_timeout_s=20, cpu_timeout_s=60)
+    world_obj = None
     if multi:
-        rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
-        assert world == n, "launch with torchrun --nproc-per-node equal to --gpus"
-        local = int(os.environ.get("LOCAL_RANK", rank))
-        torch.cuda.set_device(local)
-        import datetime
+        import torch.distributed as dist
 
-        dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=600))
         backend = "native" if args.impl == "ours" else "nccl"
         buffers = [Buffer(group=dist.group.WORLD, config=cfg, backend=backend)]
     else:
-        rank, local = 0, 0
-        torch.cuda.set_device(0)
-        if args.impl != "ours":
-            print(json.dumps({"impl": args.impl, "unavailable": "the NCCL baseline needs at least two ranks"}))
-            return
         from afdep_b200.parallel.loopback import LoopbackWorld
 
         world_obj = LoopbackWorld(cfg, gpu_timeout_s=20.0)
         buffers = world_obj.buffers
-    dev = torch.device("cuda", local)
 
-    # ---- per-rank state: pinned host inputs, device inputs, identity-expert rows ----------
+    # ---- per-rank state: pinned host inputs, two device input sets, expert weights ---------
     state = []
     for buf in buffers:
         s = {"buf": buf}
         if buf.role == "attention":
-            x, ids, w, scale = synthetic.random_batch(cfg, T, seed=1000 + buf.role_rank, zipf_s=spec["zipf"])
+            x, ids, w, scale = synthetic.random_batch(cfg, T, seed=1000 + buf.role_rank, zipf_s=spec["zipf"], pow2_scales=pow2)
             s["host"] = [t.pin_memory() if t is not None else None for t in (x, ids, w, scale)]
-            s["dev"] = [t.to(dev) if t is not None else None for t in s["host"]]
+            s["dev"] = [[t.to(dev) if t is not None else None for t in s["host"]] for _ in range(2)]
             s["ids_cpu"] = ids
-        elif "intermediate" in spec:
+        elif experts_on:
             from afdep_b200.models.moe_layer import ExpertWeights
 
-            s["weights"] = ExpertWeights.random(
-                cfg.experts_per_rank, cfg.hidden_size, spec["intermediate"], mode=args.expert_weights, down=args.expert_down, seed=7 + buf.role_rank, device=dev
-            )
+            s["weights"] = ExpertWeights.random(cfg.experts_per_rank, cfg.hidden_size, spec["intermediate"], mode=args.expert_weights,
+                                                down=args.expert_down, seed=7 + buf.role_rank, device=dev,
+                                                scale_format="pow2" if pow2 else "fp32")
         else:
             s["rows"] = torch.zeros((cfg.receive_rows(T), cfg.hidden_size), dtype=torch.bfloat16, device=dev)
+        s["host_result"] = torch.zeros(1, dtype=torch.float32).pin_memory()
         state.append(s)
 
     # wire bytes per step (both directions) from the routes: one record per (token, FFN rank)
     el = cfg.experts_per_rank
-    per_ffn = [0] * ffn          # records this process's attention ranks send to each FFN rank
-    egress = []                  # records leaving each local attention rank
+    per_ffn = [0] * ffn
+    egress = []
     for s in state:
         if "ids_cpu" in s:
             ids = s["ids_cpu"]
@@ -248,198 +297,300 @@ def main() -> None:
             mine = [int((dest == f).any(dim=1).sum()) for f in range(ffn)]
             per_ffn = [p + m for p, m in zip(per_ffn, mine)]
             egress.append(sum(mine))
-    if multi:
-        gathered = [None] * n
-        dist.all_gather_object(gathered, (per_ffn, egress))
-        per_ffn = [sum(g[0][f] for g in gathered) for f in range(ffn)]
-        egress = [e for g in gathered for e in g[1]]
+    gathered = env.gather((per_ffn, egress))
+    per_ffn = [sum(g[0][f] for g in gathered) for f in range(ffn)]
+    egress = [e for g in gathered for e in g[1]]
     records = sum(per_ffn)
     row_out = cfg.hidden_size * (1 if cfg.is_fp8 else 2) + (cfg.scale_groups * 4 if cfg.is_fp8 else 0)
     row_back = cfg.hidden_size * 2
     wire_bytes = records * (row_out + row_back)
-    # NVLink roofline: bytes through the busiest port (an attention rank's egress or an FFN
-    # rank's ingress on dispatch, the reverse on combine) over the measured 770 GB/s per direction.
     busiest = max(max(egress, default=0), max(per_ffn, default=0))
-    roofline = {
-        "busiest_port_records": busiest,
-        "dispatch_us_at_770GBs": round(busiest * row_out / 770e9 * 1e6, 2),
-        "combine_us_at_770GBs": round(busiest * row_back / 770e9 * 1e6, 2),
-        "dispatch_us_at_900GBs_nominal": round(busiest * row_out / 900e9 * 1e6, 2),
-        "combine_us_at_900GBs_nominal": round(busiest * row_back / 900e9 * 1e6, 2),
-        "note": "colocated ranks share one GPU: no NVLink, HBM-bound" if not multi else "",
-    }
 
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
     ordered = sorted(state, key=lambda s: 0 if s["buf"].role == "attention" else 1)
 
     def barrier_all():
         if multi:
-            buffers[0]._t._nb.barrier() if args.impl == "ours" else dist.barrier()
+            if args.impl == "ours":
+                buffers[0]._t._nb.barrier()
+            else:
+                import torch.distributed as dist
 
-    phase_log: dict[str, list] = {"dispatch": [], "receive": [], "experts": [], "reply": [], "collect": []}
+                dist.barrier()
 
-    def mark(name, fn, record):
-        if not record:
-            return fn()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        out = fn()
-        b.record()
-        phase_log[name].append((a, b))
-        return out
-
-    def step(copy_inputs: bool, record: bool = False):
-        """One exchange in dependency order; returns the collected output on attention ranks."""
-        result = None
+    def step(which: int = 0):
+        """One exchange in dependency order with input set ``which``; leaves a 1-element checksum
+        of the rank's result in s["sum"]."""
         for s in ordered:
             if s["buf"].role == "attention":
-                if copy_inputs:
-                    for d, h in zip(s["dev"], s["host"]):
-                        if d is not None:
-                            d.copy_(h, non_blocking=True)
-                x, ids, w, scale = s["dev"]
-                mark("dispatch", lambda: s["buf"].source_dispatch(x, ids, w, scale, bucket=T), record)
+                x, ids, w, scale = s["dev"][which]
+                s["buf"].source_dispatch(x, ids, w, scale, bucket=T)
         for s in ordered:
             if s["buf"].role == "ffn":
-                rec = mark("receive", lambda: s["buf"].worker_receive(bucket=T), record)
-                if "weights" in s:
-                    from afdep_b200.models.moe_layer import run_experts
-
-                    rows = mark("experts", lambda: run_experts(rec, s["weights"], cfg.expert_alignment), record)
+                if experts_on and fused:
+                    rec, _ = s["buf"].worker_serve_fused(s["weights"], bucket=T)
                 else:
-                    rows = rec.recv_x if not cfg.is_fp8 else s["rows"]
-                s["psum"] = rec.recv_count_psum
-                mark("reply", lambda: s["buf"].worker_reply(rows, rec.receipt), record)
+                    rec = s["buf"].worker_receive(bucket=T)
+                    if experts_on:
+                        from afdep_b200.models.moe_layer import run_experts
+
+                        rows = run_experts(rec, s["weights"], cfg.expert_alignment)
+                    else:
+                        rows = rec.recv_x if not cfg.is_fp8 else s["rows"]
+                    s["buf"].worker_reply(rows, rec.receipt)
+                s["result"] = rec.recv_count_psum
         for s in ordered:
             if s["buf"].role == "attention":
-                s["out"] = mark("collect", lambda: s["buf"].source_collect(), record)
-                result = s["out"]
-        return result
+                s["out"] = s["buf"].source_collect()
+                s["result"] = s["out"]
+
+    def read_back():
+        """The step's result as the host sees it: a checksum per rank, copied to pinned memory."""
+        for s in state:
+            s["host_result"].copy_(s["result"].sum(dtype=torch.float32).reshape(1), non_blocking=True)
 
     def count_launches():
         return sum(int(s["buf"].stats().get("launches", 0)) for s in state)
 
-    # kernels of this library per exchange on this process, counted on one eager warm-up step
     before_one = count_launches()
-    step(False)
+    step()
     torch.cuda.synchronize()
     launches_per_step = count_launches() - before_one
-    if multi:
-        dist.barrier()
+    env.host_barrier()
 
+    # ---- CUDA graphs: one per input set, plus a traced one for the phase times ---------------
     use_graph = args.impl == "ours" and not args.eager
-    graph = None
+    side = torch.cuda.Stream()
+    kernel_graph, graphs, traced_graph, traces = None, [None, None], None, []
+
+    def capture(which, with_read_back):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            step(which)
+            if with_read_back:
+                read_back()
+        return g
+
     if use_graph:
-        side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             for _ in range(2):
-                step(False)
+                step()
         torch.cuda.synchronize()
-        if multi:
-            dist.barrier()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=side):
-            step(False)
+        env.host_barrier()
+        kernel_graph = capture(0, False)
+        if with_e2e:
+            graphs = [capture(0, True), capture(1, True)]
+        traces = [(s["buf"].rank, s["buf"]._t._nb.trace(True)) for s in state]
+        traced_graph = capture(0, False)
+        for s in state:
+            s["buf"]._t._nb.trace(False)
         torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        env.host_barrier()
 
-    def timed(copy_inputs: bool, steps: int, warmup: int):
-        """Device time of each step.  The kernel-only pass enqueues every step back to back (the
-        L2 flush and the cross-rank barrier sit between the event pairs, outside them) and
-        synchronises once; the end-to-end pass waits for each step's result on the host."""
+    def run_step(which=0):
+        """A step as the end-to-end passes issue it: the exchange and the read-back of its result."""
+        if graphs[which] is not None:
+            graphs[which].replay()
+        else:
+            step(which)
+            read_back()
+
+    # ---- kernel-only timing: rounds of `steps` exchanges ---------------------------------------
+    def timed_round(count):
         pairs = []
-        host_result = torch.zeros(1, dtype=torch.float32).pin_memory()
-        for i in range(warmup + steps):
-            flush.fill_(i & 0xFF)
+        for i in range(count):
+            env.flush.fill_(i & 0xFF)
             barrier_all()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            if graph is not None and not copy_inputs:
-                graph.replay()
+            if kernel_graph is not None:
+                kernel_graph.replay()
             else:
-                out = step(copy_inputs, record=(i >= warmup and not copy_inputs))
-                if copy_inputs:
-                    src = out.float().sum().reshape(1) if out is not None else state[0]["psum"].float().sum().reshape(1)
-                    host_result.copy_(src, non_blocking=True)
+                step(0)
             e1.record()
-            if copy_inputs:
-                e1.synchronize()
             pairs.append((e0, e1))
         torch.cuda.synchronize()
-        return [a.elapsed_time(b) for a, b in pairs[warmup:]]
+        return [a.elapsed_time(b) for a, b in pairs]
 
-    traces = []
-    if args.trace and args.impl == "ours":
-        traces = [(s["buf"].rank, s["buf"]._t._nb.trace(True)) for s in state]
-    torch.cuda.synchronize()
-    if multi:
-        dist.barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
+    timed_round(warmup)
+    if sampler is not None and env.rank == 0:
         sampler.start()
-    torch.cuda.synchronize()
     t_wall0 = time.perf_counter()
-    times = timed(False, args.steps, args.warmup)
+    first = sum(timed_round(steps))
+    # every rank must run the same number of rounds: agree on it from the slowest rank's first round
+    first_max = max(env.gather(first))
+    rounds = max(1, min(400, int(MIN_TIMED_SECONDS * 1e3 / max(first_max, 1e-3)) + 1))
+    round_ms = [first] + [sum(timed_round(steps)) for _ in range(rounds - 1)]
     torch.cuda.synchronize()
     t_wall1 = time.perf_counter()
-    clocks_timed_region_samples = len(sampler.samples) if rank == 0 else 0
-    launches = launches_per_step * args.steps      # every timed step replays / launches the same kernels
-    if graph is not None:
-        # per-call device times come from a short eager pass; the headline stays the graph replay
-        saved, graph = graph, None
-        timed(False, min(args.steps, 10), 2)
-        graph = saved
-    e2e_times = None
-    if not args.no_e2e:
-        e2e_times = timed(True, args.steps, max(3, args.warmup))
+    samples_in_region = len(sampler.samples) if sampler is not None and env.rank == 0 else 0
+    all_rounds = env.gather(round_ms)
+    per_round = [max(r[i] for r in all_rounds) for i in range(len(round_ms))]      # max over ranks, round by round
+    ms_per_step = percentile(per_round, 0.5) / steps
+    launches = sum(env.gather(launches_per_step * steps * len(round_ms)))
 
-    # the sampler keeps running through the eager and end-to-end passes: all of it is under load
-    clocks = sampler.stop() if rank == 0 else None
-    if clocks is not None:
-        clocks["samples_in_device_timed_region"] = clocks_timed_region_samples
+    # ---- phases: kernel durations from one traced graph replay ------------------------------------
+    phases, trace_lines = {}, []
+    if traced_graph is not None:
+        env.flush.fill_(1)
+        barrier_all()
+        traced_graph.replay()
+        torch.cuda.synchronize()
+        names = ["dispatch", "receive", "reply", "collect"]
+        local_phase = {}
+        for r, tr in traces:
+            tr = tr.cpu()
+            for k, kname in enumerate(names):
+                t = tr[k]
+                used = t[:, 0] > 0
+                if not used.any():
+                    continue
+                t = t[used]
+                s0 = int(t[:, 0].min())
+                dur = (int(t[:, 2].max()) - s0) / 1e3
+                local_phase[kname] = max(local_phase.get(kname, 0.0), dur)
+                if trace_print:
+                    p1 = (int(t[:, 1].max()) - s0) / 1e3 if (t[:, 1] > 0).any() else float("nan")
+                    trace_lines.append(
+                        f"rank {r} {kname:9s} ctas={int(used.sum()):3d} start_ns={s0 % 10**9:9d} phase1_end={p1:7.1f}us "
+                        f"first_cta_end={(int(t[:, 2].min()) - s0) / 1e3:7.1f}us last_cta_end={dur:7.1f}us"
+                    )
+        for part in env.gather(local_phase):
+            for kname, dur in part.items():
+                phases[kname + "_us"] = round(max(phases.get(kname + "_us", 0.0), dur), 2)
+        phases["source"] = "device time stamps of one traced graph replay: first CTA start to last CTA end of each kernel, maximum over ranks"
+    if experts_on:
+        # time of the FFN rank's part (receive + experts + reply) from events around it in an eager step
+        ev = []
+        for _ in range(3):
+            env.flush.fill_(2)
+            barrier_all()
+            for s in ordered:
+                if s["buf"].role == "attention":
+                    x, ids, w, scale = s["dev"][0]
+                    s["buf"].source_dispatch(x, ids, w, scale, bucket=T)
+            for s in ordered:
+                if s["buf"].role == "ffn":
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record()
+                    if fused:
+                        s["buf"].worker_serve_fused(s["weights"], bucket=T)
+                    else:
+                        from afdep_b200.models.moe_layer import run_experts
 
-    def reduce_max(values):
-        total = sum(values)
-        if multi:
-            allv = [None] * n
-            dist.all_gather_object(allv, total)
-            return max(allv)
-        return total
+                        rec = s["buf"].worker_receive(bucket=T)
+                        s["buf"].worker_reply(run_experts(rec, s["weights"], cfg.expert_alignment), rec.receipt)
+                    b.record()
+                    ev.append((a, b))
+            for s in ordered:
+                if s["buf"].role == "attention":
+                    s["buf"].source_collect()
+        torch.cuda.synchronize()
+        local = min((a.elapsed_time(b) for a, b in ev), default=0.0) * 1e3
+        phases["ffn_receive_experts_reply_us"] = round(max(env.gather(local)), 2)
 
-    # mean device time of each role call (kernel plus its waits), maximum over ranks
-    phases = {}
-    for name, pairs in phase_log.items():
-        local_us = 1e3 * sum(a.elapsed_time(b) for a, b in pairs) / max(1, len(pairs)) if pairs else 0.0
-        if multi:
-            allp = [None] * n
-            dist.all_gather_object(allp, local_us)
-            local_us = max(allp)
-        phases[name + "_us"] = round(local_us, 2)
+    # ---- end to end: inputs from pinned host memory and a result read back, every step ----------
+    e2e = None
+    if with_e2e:
+        copy_stream = torch.cuda.Stream()
+        h2d = sum(sum(t.numel() * t.element_size() for t in s["host"] if t is not None) for s in state if "host" in s)
+        h2d = sum(env.gather(h2d))
 
-    total_ms = reduce_max(times)
-    ms_per_step = total_ms / args.steps
-    if multi:
-        alll = [None] * n
-        dist.all_gather_object(alll, launches)
-        launches = sum(alll)
+        def copy_inputs(which, stream):
+            with torch.cuda.stream(stream):
+                for s in state:
+                    if "host" in s:
+                        for d, h in zip(s["dev"][which], s["host"]):
+                            if d is not None:
+                                d.copy_(h, non_blocking=True)
+
+        def e2e_serial(count):
+            cur = torch.cuda.current_stream()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(count):
+                copy_inputs(0, cur)
+                run_step(0)
+                cur.synchronize()               # the host reads the step's result before it issues the next step
+            e1.record()
+            e1.synchronize()
+            return e0.elapsed_time(e1)
+
+        def e2e_pipelined(count):
+            cur = torch.cuda.current_stream()
+            done = [torch.cuda.Event(), torch.cuda.Event()]       # input set filled
+            free = [torch.cuda.Event(), torch.cuda.Event()]       # input set no longer read
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            copy_stream.wait_event(e0)
+            copy_inputs(0, copy_stream)
+            done[0].record(copy_stream)
+            for i in range(count):
+                b = i & 1
+                cur.wait_event(done[b])
+                if i + 1 < count:
+                    if i >= 1:
+                        copy_stream.wait_event(free[b ^ 1])
+                    copy_inputs(b ^ 1, copy_stream)          # next step's inputs travel while this step runs
+                    done[b ^ 1].record(copy_stream)
+                run_step(b)
+                free[b].record(cur)
+                cur.synchronize()
+            e1.record()
+            e1.synchronize()
+            return e0.elapsed_time(e1)
+
+        for fn in (e2e_serial, e2e_pipelined):
+            barrier_all()
+            fn(max(3, warmup))
+        e2e_rounds = max(1, min(rounds, 50))
+        serial_ms, piped_ms = [], []
+        for _ in range(e2e_rounds):
+            barrier_all()
+            torch.cuda.synchronize()
+            serial_ms.append(e2e_serial(steps))
+            barrier_all()
+            torch.cuda.synchronize()
+            piped_ms.append(e2e_pipelined(steps))
+        serial = percentile([max(r[i] for r in env.gather(serial_ms)) for i in range(e2e_rounds)], 0.5) / steps
+        piped = percentile([max(r[i] for r in env.gather(piped_ms)) for i in range(e2e_rounds)], 0.5) / steps
+        e2e = {
+            "value": round(wire_bytes / (piped * 1e-3) / 1e9, 3),
+            "unit": "GB/s",
+            "ms_per_step": round(piped, 5),
+            "h2d_bytes_per_step": h2d,
+            "d2h_bytes_per_step": 4 * len(env.gather(0)) * (1 if multi else len(state)),
+            "mode": "step n+1's inputs are copied on a second stream while step n runs; the host reads every step's checksum before issuing the next",
+            "serial": {"value": round(wire_bytes / (serial * 1e-3) / 1e9, 3), "ms_per_step": round(serial, 5),
+                       "mode": "copy, exchange and read-back back to back on one stream"},
+            "rounds": e2e_rounds,
+        }
+
     value = wire_bytes / (ms_per_step * 1e-3) / 1e9
+    roof_900 = busiest * (row_out + row_back) / (NVLINK_NOMINAL_GBS * 1e9) * 1e6
+    roof_meas = busiest * (row_out + row_back) / (NVLINK_MEASURED_GBS * 1e9) * 1e6
     result = {
         "metric": "dispatch+combine aggregate wire GB/s (all ranks, max-over-ranks step time)",
         "value": round(value, 3),
         "unit": "GB/s",
         "n_gpus": n,
-        "steps": args.steps,
-        "warmup": args.warmup,
+        "steps": steps,
+        "warmup": warmup,
         "ms_per_step": round(ms_per_step, 5),
         "us_per_exchange": round(ms_per_step * 1e3, 2),
+        "per_rank_GBs": round(value / attn, 3),
+        "rounds": len(per_round),
+        "us_per_exchange_p10": round(percentile(per_round, 0.1) / steps * 1e3, 2),
+        "us_per_exchange_p90": round(percentile(per_round, 0.9) / steps * 1e3, 2),
         "higher_is_better": True,
         "scaling": "weak",
         "vs_baseline": None,
         "dtype": "fp8(e4m3)+bf16" if cfg.is_fp8 else "bf16",
-        "data": "synthetic (seeded N(0,1) activations, distinct top-k routes, softmax weights; no weights involved)",
+        "data": "synthetic (seeded N(0,1) activations, distinct top-k routes, softmax weights" + ("; random-init N(0,0.02) expert weights)" if experts_on else "; no weights involved)"),
         "impl": args.impl,
         "config": {
-            "model": f"AFD MoE exchange, BASELINE config {args.config}",
+            "model": f"AFD MoE exchange, config {name}",
             "global_batch": T * attn,
             "seq_len": 1,
             "parallelism": f"{attn}A+{ffn}F" + (" colocated on one GPU" if not multi else ""),
@@ -449,94 +600,83 @@ def main() -> None:
             "tokens_per_attention_rank": T,
             "payload": cfg.payload,
             "routing": "zipf(1.1)" if spec["zipf"] else "uniform",
-            "l2": "flushed between steps (256 MiB fill)",
-            "mode": "cuda-graph replay of complete exchanges (phases and e2e: eager launches)" if graph is not None else "eager",
+            "l2": "flushed between steps (256 MiB fill); e2e: inputs arrive from host memory every step",
+            "mode": "cuda-graph replay of complete exchanges" if use_graph else "eager",
             "wire_bytes_per_step": wire_bytes,
             "tokens_per_s": round(T * attn / (ms_per_step * 1e-3), 1),
-            "per_attention_rank_GBs": round(value / attn, 3),
         },
-        "expert_tflops": (
-            round(6.0 * T * attn * cfg.top_k * cfg.hidden_size * spec["intermediate"] / (ms_per_step * 1e-3) / 1e12, 2)
-            if "intermediate" in spec
-            else None
-        ),
-        "expert_weights": (
-            {"gate_up": args.expert_weights, "down": args.expert_down or args.expert_weights}
-            if "intermediate" in spec
-            else None
+        "expert_tflops": (round(6.0 * T * attn * cfg.top_k * cfg.hidden_size * spec["intermediate"] / (ms_per_step * 1e-3) / 1e12, 2) if experts_on else None),
+        "experts": (
+            {"gate_up": args.expert_weights, "down": args.expert_down or args.expert_weights,
+             "block_scales": ("powers of two, applied by the tensor core (deviation from plain amax/448 fp32 scales: each scale rounded up to 2^k)"
+                              if pow2 else "fp32 amax/448, promoted through registers") if args.expert_weights == "fp8" else None,
+             "fused_receive": fused}
+            if experts_on else None
         ),
         "phases": phases,
-        "roofline": dict(
-            roofline,
-            fraction_of_nvlink_roofline=round((roofline["dispatch_us_at_770GBs"] + roofline["combine_us_at_770GBs"]) / (ms_per_step * 1e3), 3),
-        ),
-        "clocks": clocks,
+        "roofline": {
+            "busiest_port_records": busiest,
+            "us_at_900GBs_nominal": round(roof_900, 2),
+            "us_at_measured_rate": round(roof_meas, 2),
+            "measured_rate_GBs": NVLINK_MEASURED_GBS,
+            "fraction_at_900GBs_nominal": round(roof_900 / (ms_per_step * 1e3), 3),
+            "fraction_at_measured_rate": round(roof_meas / (ms_per_step * 1e3), 3),
+            "note": "colocated ranks share one GPU: no NVLink, HBM-bound" if not multi else "bytes through the busiest port, both directions",
+        },
         "gpu_launches": launches,
         "wall_s_timed_region": round(t_wall1 - t_wall0, 3),
+        "clock_samples_in_timed_region": samples_in_region,
     }
-    if e2e_times is not None:
-        e2e_ms = reduce_max(e2e_times) / args.steps
-        hi = sum(sum(t.numel() * t.element_size() for t in s["host"] if t is not None) for s in state if "host" in s)
-        if multi:
-            allh = [None] * n
-            dist.all_gather_object(allh, hi)
-            hi = sum(allh)
-        result["e2e"] = {
-            "value": round(wire_bytes / (e2e_ms * 1e-3) / 1e9, 3),
-            "unit": "GB/s",
-            "ms_per_step": round(e2e_ms, 5),
-            "h2d_bytes_per_step": hi,
-            "d2h_bytes_per_step": 4 * n,
-        }
-    if traces:
-        names = ["dispatch", "receive", "reply", "collect"]
-        lines = []
-        for r, tr in traces:
-            tr = tr.cpu()
-            for k in range(4):
-                t = tr[k]
-                used = t[:, 0] > 0
-                if not used.any():
-                    continue
-                t = t[used]
-                s0 = int(t[:, 0].min())
-                p1 = (int(t[:, 1].max()) - s0) / 1e3 if (t[:, 1] > 0).any() else float("nan")
-                lines.append(
-                    f"rank {r} {names[k]:9s} ctas={int(used.sum()):3d} start_ns={s0 % 10**9:9d} phase1_end={p1:7.1f}us "
-                    f"first_cta_end={(int(t[:, 2].min()) - s0) / 1e3:7.1f}us last_cta_end={(int(t[:, 2].max()) - s0) / 1e3:7.1f}us"
-                )
-                if k in (0, 1) and (t[:, 3] >= s0).any():
-                    col = t[:, 3][t[:, 3] >= s0]
-                    what = "counts released" if k == 0 else "counts arrived"
-                    lines.append(f"rank {r} {names[k]:9s} {what} at {(int(col.min()) - s0) / 1e3:.1f}..{(int(col.max()) - s0) / 1e3:.1f}us")
-                # progress of warp 0's first record (receive) / token (collect) per CTA, min..max over CTAs
-                detail = {1: (5, ("flag_seen", "landed", "stores_committed", "stores_complete")), 3: (6, ("flags_seen", "rows_landed", "stored"))}
-                if k in detail and tr.shape[0] > detail[k][0]:
-                    d = tr[detail[k][0]]
-                    live = d[:, 0] >= s0
-                    if live.any():
-                        parts = []
-                        for j, label in enumerate(detail[k][1]):
-                            col = d[live][:, j]
-                            col = col[col >= s0]
-                            if col.numel():
-                                parts.append(f"{label}={(int(col.min()) - s0) / 1e3:.1f}..{(int(col.max()) - s0) / 1e3:.1f}us")
-                        lines.append(f"rank {r} {names[k]:9s} first item per CTA ({int(live.sum())} CTAs): " + " ".join(parts))
-        if multi:
-            alll = [None] * n
-            dist.all_gather_object(alll, lines)
-            lines = [l for part in alll for l in part]
-        if rank == 0:
+    if e2e is not None:
+        result["e2e"] = e2e
+    if trace_print and trace_lines:
+        lines = [l for part in env.gather(trace_lines) for l in part]
+        if env.rank == 0:
             print("\n".join(lines), file=sys.stderr)
     for s in state:
         s["buf"].check()
+    graphs.clear()
+    kernel_graph = traced_graph = None
     if multi:
         buffers[0].close()
-        dist.barrier()
-        dist.destroy_process_group()
     else:
         world_obj.close()
-    if rank == 0:
+    env.host_barrier()
+    return result
+
+
+def main() -> None:
+    args = parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+    if args.gpus == 1 and args.impl != "ours":
+        print(json.dumps({"impl": args.impl, "unavailable": "the NCCL baseline needs at least two ranks"}))
+        return
+
+    env = Env(args)
+    sampler = ClockSampler(env.local)
+    result = run_config(env, args.config, steps=args.steps, warmup=args.warmup, tokens=args.tokens, with_e2e=not args.no_e2e,
+                        trace_print=args.trace, sampler=sampler)
+    if env.n == 8 and args.config == "weak" and args.impl == "ours" and not args.no_extra:
+        # the 8-GPU configurations, measured in the same run: skewed FP8 prefill, decode, end-to-end MoE layer
+        extra = {}
+        for name, k in (("3", 20), ("4", 100), ("5", 10)):
+            sub = run_config(env, name, steps=k, warmup=3, with_e2e=False)
+            extra["config" + name] = {key: sub[key] for key in ("value", "us_per_exchange", "us_per_exchange_p10", "us_per_exchange_p90", "per_rank_GBs", "rounds",
+                                                              "steps", "dtype", "config", "phases", "roofline", "expert_tflops", "experts", "gpu_launches")}
+        result["extra"] = extra
+    # the sampler runs through every pass of this invocation: all of it is under load
+    clocks = sampler.stop() if env.rank == 0 else None
+    if clocks is not None:
+        clocks["samples_in_device_timed_region"] = result.pop("clock_samples_in_timed_region", 0)
+    result["clocks"] = clocks
+    if env.multi:
+        import torch.distributed as dist
+
+        dist.barrier()
+        dist.destroy_process_group()
+    if env.rank == 0:
         print(json.dumps(result))
 
 

@@ -243,25 +243,49 @@ def _primitives(rank, world):
         g = torch.Generator().manual_seed(100 * rnd + r)
         return torch.randn(64, 128, generator=g).bfloat16()
 
-    for rnd, engine in enumerate(("sm", "copy", "copy", "sm", "copy")):
-        got = prims.all_gather(part(rank, rnd).cuda(), engine=engine)
-        torch.cuda.synchronize()
-        assert torch.equal(got.cpu(), torch.stack([part(r, rnd) for r in range(world)])), f"gather {rnd} ({engine})"
-        prims.barrier()        # nobody overwrites a slot its peers may still be reading
-    for step in range(3):
-        prims.send(part(rank, 50 + step).cuda(), (rank + 1) % world)
+    # Gathers back to back, no barrier and no host synchronisation in between, one rank dawdling
+    # before some of them: slots alternate between two sets and every result is a copy, so a fast
+    # rank can never overwrite what a slow one has not read yet.
+    results = []
+    for rnd, engine in enumerate(("sm", "copy", "copy", "sm", "copy", "sm", "sm")):
+        if rank == rnd % world:
+            torch.cuda._sleep(int(3e7))
+        results.append(prims.all_gather(part(rank, rnd).cuda(), engine=engine))
+    torch.cuda.synchronize()
+    for rnd, got in enumerate(results):
+        assert torch.equal(got.cpu(), torch.stack([part(r, rnd) for r in range(world)])), f"gather {rnd}"
+    prims.barrier()
+    # Send/recv: six messages to the next rank before a single receive is issued (the ring holds
+    # four, so sends five and six wait on the device for credits), the receiver deliberately late.
+    assert prims.inflight == 4
+    nxt, prv = (rank + 1) % world, (rank - 1) % world
+    msgs = 6
+    for step in range(prims.inflight):
+        prims.send(part(rank, 50 + step).cuda(), nxt)
+    torch.cuda._sleep(int(5e7))
+    outs = []
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):               # the credit-bound sends queue on a second stream ...
+        for step in range(prims.inflight, msgs):
+            prims.send(part(rank, 50 + step).cuda(), nxt)
+    for step in range(msgs):                    # ... while this stream drains the incoming ring
         out = torch.empty(64, 128, device="cuda", dtype=torch.bfloat16)
-        prims.recv(out, (rank - 1) % world)
-        torch.cuda.synchronize()
-        assert torch.equal(out.cpu(), part((rank - 1) % world, 50 + step))
+        prims.recv(out, prv)
+        outs.append(out)
+    torch.cuda.synchronize()
+    for step, out in enumerate(outs):
+        assert torch.equal(out.cpu(), part(prv, 50 + step)), f"message {step}"
+    prims.barrier()
     rows, width = 32, 128
     prims.table_shard(rows, width, torch.bfloat16).copy_(part(rank, 99)[:rows].cuda())
     prims.barrier()
     idx = torch.tensor([0, rows * world - 1, rows, 5, rows + 7], device="cuda")
-    got = prims.fetch_rows(idx, rows, width, torch.bfloat16)
+    handle = prims.fetch_rows_start(idx, rows, width, torch.bfloat16)      # issued on a side stream ...
+    busy = torch.randn(512, 512, device="cuda") @ torch.randn(512, 512, device="cuda")
+    got = handle.wait()                                                     # ... joined here
     torch.cuda.synchronize()
     table = torch.cat([part(r, 99)[:rows] for r in range(world)])
-    assert torch.equal(got.cpu(), table[idx.cpu()])
+    assert torch.equal(got.cpu(), table[idx.cpu()]) and bool(torch.isfinite(busy).all())
     buf.check()
     dist.barrier()
     buf.close()

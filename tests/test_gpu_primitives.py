@@ -18,7 +18,7 @@ def world():
     from afdep_b200.parallel.loopback import LoopbackWorld
 
     cfg = Config(8, 256, 8, 2, 2, 2)
-    w = LoopbackWorld(cfg, gpu_timeout_s=2.0, aux_bytes=4 << 20)
+    w = LoopbackWorld(cfg, gpu_timeout_s=2.0, aux_bytes=8 << 20)
     yield w
     w.close()
 
@@ -54,19 +54,52 @@ def test_all_gather_copy_engine_and_mixed(world):
 
 
 def test_send_recv_ring_with_credits(world):
+    """Four messages per pair in flight before the first receive (the ring's depth), twice over,
+    so the second batch of sends runs on credits returned by the first batch of receives."""
     prims = [HeapPrimitives(b) for b in world.buffers]
     n = len(prims)
-    for step in range(4):      # more messages than slots: every send needs the previous credit
-        msgs = [torch.randn(1024, device="cuda") + r for r in range(n)]
-        for r, p in enumerate(prims):
-            p.send(msgs[r], (r + 1) % n)
-        for r, p in enumerate(prims):
-            out = torch.empty(1024, device="cuda")
-            p.recv(out, (r - 1) % n)
-            torch.cuda.synchronize()
-            assert torch.equal(out, msgs[(r - 1) % n])
+    depth = prims[0].inflight
+    assert depth == 4
+    for batch in range(2):
+        msgs = [[torch.randn(3000, device="cuda") + 10 * r + k for k in range(depth)] for r in range(n)]
+        for k in range(depth):
+            for r, p in enumerate(prims):
+                p.send(msgs[r][k], (r + 1) % n)
+        for k in range(depth):
+            for r, p in enumerate(prims):
+                out = torch.empty(3000, device="cuda")
+                p.recv(out, (r - 1) % n)
+                torch.cuda.synchronize()
+                assert torch.equal(out, msgs[(r - 1) % n][k]), (batch, k, r)
     for b in world.buffers:
         b.check()
+
+
+def test_large_message_through_the_copy_pipeline(world):
+    """A message of many 32 KB chunks over several CTAs, with a ragged tail."""
+    prims = [HeapPrimitives(b) for b in world.buffers]
+    nbytes = min(prims[0].message_bytes, (200 << 10) + 48)
+    src = torch.randint(0, 255, (nbytes,), device="cuda", dtype=torch.uint8)
+    out = torch.zeros_like(src)
+    prims[0].send(src, 2)
+    prims[2].recv(out, 0)
+    torch.cuda.synchronize()
+    assert torch.equal(out, src)
+    world.buffers[0].check()
+
+
+def test_back_to_back_gathers_without_barrier(world):
+    prims = [HeapPrimitives(b) for b in world.buffers]
+    results, inputs = [], []
+    for rnd in range(5):
+        parts = [torch.randn(24, 64, device="cuda").bfloat16() + rnd for _ in range(4)]
+        inputs.append(torch.stack(parts))
+        handles = [p.all_gather_start(t) for p, t in zip(prims, parts)]
+        results.append([h.wait() for h in handles])
+    torch.cuda.synchronize()
+    for want, got in zip(inputs, results):
+        for g in got:
+            assert torch.equal(g, want)
 
 
 def test_fetch_rows(world):
@@ -78,9 +111,22 @@ def test_fetch_rows(world):
     torch.cuda.synchronize()
     idx = torch.randint(0, 4 * rows, (300,), device="cuda")
     idx[0] = -5                      # out of range: a zero row, not a wild read
+    want = table[idx.clamp(min=0)]
+    want[0] = 0
     for p in prims:
         got = p.fetch_rows(idx, rows, width, torch.bfloat16)
         torch.cuda.synchronize()
-        want = table[idx.clamp(min=0)]
-        want[0] = 0
         assert torch.equal(got, want)
+    # issue / wait split: the fetch runs on a side stream while this stream does other work
+    handle = prims[1].fetch_rows_start(idx, rows, width, torch.bfloat16)
+    other = torch.randn(256, 256, device="cuda") @ torch.randn(256, 256, device="cuda")
+    got = handle.wait()
+    torch.cuda.synchronize()
+    assert torch.equal(got, want) and bool(torch.isfinite(other).all())
+    # rows wider than the per-warp bulk buffer take the plain-load path
+    wide = prims[0].table_shard(2, 8192, torch.bfloat16)
+    wide.copy_(torch.arange(2 * 8192, device="cuda").view(2, 8192).bfloat16())
+    torch.cuda.synchronize()
+    got = prims[3].fetch_rows(torch.tensor([1, 0], device="cuda"), 2, 8192, torch.bfloat16)
+    torch.cuda.synchronize()
+    assert torch.equal(got, wide[[1, 0]])
