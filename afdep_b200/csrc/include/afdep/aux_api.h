@@ -27,7 +27,8 @@ struct AuxSeq {            // device-resident sequence numbers (never reset)
     unsigned* gather;      // exchanges of all_gather completed
     unsigned* sent;        // [kMaxRanks] messages sent to each peer
     unsigned* received;    // [kMaxRanks] messages consumed from each peer
-    unsigned* ticket;      // CTA completion counter
+    unsigned* ticket;      // [3] CTA completion counters: gather push, send, receive (a send may overlap a receive;
+                           // two sends, or two receives, of one Buffer must not overlap each other)
 };
 
 // Copy `bytes` from `src` into slot [rank] of every peer's data area and raise the gather flag.

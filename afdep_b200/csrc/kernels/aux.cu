@@ -92,7 +92,7 @@ __global__ void __launch_bounds__(kThreads) allgather_push_kernel(const RankCtx 
             poison(wc);
         }
     }
-    if (last_cta(seq.ticket) && threadIdx.x < W) {
+    if (last_cta(seq.ticket + 0) && threadIdx.x < W) {
         ptx::fence_acq_rel_sys();
         ptx::st_relaxed_sys(aux_signal(c, threadIdx.x, c.rank), ep);
     }
@@ -156,7 +156,7 @@ __global__ void __launch_bounds__(kThreads) p2p_send_kernel(const RankCtx c, con
         s_ok = ok;
     }
     __syncthreads();
-    if (last_cta(seq.ticket) && threadIdx.x == 0) {
+    if (last_cta(seq.ticket + 1) && threadIdx.x == 0) {
         if (s_ok) {
             ptx::fence_acq_rel_sys();
             ptx::st_relaxed_sys(aux_signal(c, dst, 8 + c.rank), n);
@@ -188,7 +188,7 @@ __global__ void __launch_bounds__(kThreads) p2p_recv_kernel(const RankCtx c, con
         s_ok = ok;
     }
     __syncthreads();
-    if (last_cta(seq.ticket) && threadIdx.x == 0) {
+    if (last_cta(seq.ticket + 2) && threadIdx.x == 0) {
         if (s_ok) {
             ptx::fence_acq_rel_sys();
             ptx::st_relaxed_sys(aux_signal(c, src_rank, 16 + c.rank), n);     // credit: the slot is free again

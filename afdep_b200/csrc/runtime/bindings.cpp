@@ -522,6 +522,13 @@ public:
         auto* base = static_cast<unsigned char*>(heap_->local()) + geo_.aux_off + kAuxSignalBytes;
         return torch::from_blob(base, {aux_data_bytes()}, torch::TensorOptions().dtype(torch::kUInt8).device(torch::kCUDA, device_));
     }
+    // Snapshot of this rank's 24 signal words (gather flags, send flags, credits), for diagnostics.
+    torch::Tensor aux_signals() {
+        live();
+        auto* base = static_cast<unsigned char*>(heap_->local()) + geo_.aux_off;
+        auto view = torch::from_blob(base, {24}, torch::TensorOptions().dtype(torch::kInt32).device(torch::kCUDA, device_));
+        return view.clone();
+    }
     void allgather_push(const torch::Tensor& t) {
         live();
         const size_t bytes = check_aux_tensor(t, aux_slot_bytes());
@@ -674,10 +681,12 @@ private:
         TORCH_CHECK((int64_t)bytes <= slot, "tensor larger than its slot of the auxiliary region (raise aux_bytes)");
         return bytes;
     }
-    // One CTA (one copy engine) per 128 KB, at most the communication SM budget.
+    // One CTA (one SM's copy engine) per 64 KB, up to the whole device: these primitives run on their
+    // own, not beside a compute kernel, and a remote store takes microseconds to drain, so the link is
+    // only filled when many SMs have stores in flight.
     int aux_ctas(size_t bytes) const {
-        const int want = (int)((bytes + 131071) / 131072);
-        return want < 1 ? 1 : (want > num_sms_ ? num_sms_ : want);
+        const int want = (int)((bytes + 65535) / 65536);
+        return want < 1 ? 1 : (want > device_sms_ ? device_sms_ : want);
     }
 
     static constexpr size_t kHostBlockBytes = 8192;
@@ -1039,6 +1048,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         .def("p2p_slot_bytes", &NativeBuffer::p2p_slot_bytes)
         .def("p2p_inflight", &NativeBuffer::p2p_inflight)
         .def("aux_view", &NativeBuffer::aux_view)
+        .def("aux_signals", &NativeBuffer::aux_signals)
         .def("allgather_push", &NativeBuffer::allgather_push)
         .def("enable_expert_stats", &NativeBuffer::enable_expert_stats)
         .def("allgather_push_copy", &NativeBuffer::allgather_push_copy)

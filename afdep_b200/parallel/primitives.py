@@ -72,7 +72,9 @@ class HeapPrimitives:
     # ---- neighbour send / recv -------------------------------------------------------------
     def send(self, tensor: torch.Tensor, dst: int) -> None:
         """One message to ``dst``.  Up to ``inflight`` messages may be on their way; the kernel of
-        message ``n`` waits (bounded, on the device) until ``dst`` has consumed message ``n - inflight``."""
+        message ``n`` waits (bounded, on the device) until ``dst`` has consumed message ``n - inflight``.
+        Sends of one Buffer must be stream-ordered among themselves, receives likewise (they number
+        their messages on the device); a send may run beside a receive on another stream."""
         self._nb.p2p_send(tensor, int(dst))
 
     def recv(self, out: torch.Tensor, src: int) -> torch.Tensor:

