@@ -39,9 +39,10 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const __nv_bfloat16*
             if (bits & 0x7fffffu) ++e;
             s = __uint_as_float(min(max(e, 1u), 253u) << 23);
         }
-        const float inv = 1.f / s;
-        const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a.x * inv, a.y * inv), __NV_SATFINITE, __NV_E4M3);
-        const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(b.x * inv, b.y * inv), __NV_SATFINITE, __NV_E4M3);
+        // true divisions: a value that sits on an e4m3 rounding boundary must land on the same side
+        // as in the reference quantiser (the kernel is bound by memory, not by these)
+        const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a.x / s, a.y / s), __NV_SATFINITE, __NV_E4M3);
+        const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(make_float2(b.x / s, b.y / s), __NV_SATFINITE, __NV_E4M3);
         *reinterpret_cast<uint32_t*>(q + off) = (uint32_t)lo | ((uint32_t)hi << 16);
         if (lane == 0) scale[(size_t)row * ss0 + (size_t)gidx * ss1] = s;
     }
