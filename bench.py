@@ -68,6 +68,7 @@ def parse_args():
                    help="config 5, FP8: block scales rounded up to powers of two and applied by the tensor core (default), or arbitrary fp32 scales promoted through registers")
     p.add_argument("--unfused", action="store_true", help="config 5: worker_receive -> experts -> worker_reply as separate calls")
     p.add_argument("--no-extra", action="store_true", help="--gpus 8: skip the sub-results for configs 3, 4 and 5")
+    p.add_argument("--max-rounds", type=int, default=400, help="upper bound on the rounds of K steps (1 for a profiler capture)")
     p.add_argument("--tokens", type=int, default=0, help="override tokens per attention rank")
     p.add_argument("--num-sms", type=int, default=0)
     p.add_argument("--graph", action="store_true", help="(default for --impl ours) replay each timed step from a CUDA graph")
@@ -420,7 +421,7 @@ def run_config(env: Env, name: str, *, steps: int, warmup: int, tokens: int = 0,
     first = sum(timed_round(steps))
     # every rank must run the same number of rounds: agree on it from the slowest rank's first round
     first_max = max(env.gather(first))
-    rounds = max(1, min(400, int(MIN_TIMED_SECONDS * 1e3 / max(first_max, 1e-3)) + 1))
+    rounds = max(1, min(args.max_rounds, int(MIN_TIMED_SECONDS * 1e3 / max(first_max, 1e-3)) + 1))
     round_ms = [first] + [sum(timed_round(steps)) for _ in range(rounds - 1)]
     torch.cuda.synchronize()
     t_wall1 = time.perf_counter()
