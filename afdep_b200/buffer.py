@@ -138,6 +138,7 @@ class ElasticBuffer:
         self.role_aware, self.ffn_ranks = role_aware, ffn_ranks
         self.backend = backend
         self._owner, self._pending, self._closed = object(), None, False
+        self.last_event = None      # EventHandle of the last call made with async_finish=True
         self._transport = None
         settings = {
             "capacity": capacity_tokens_per_rank,
@@ -272,7 +273,8 @@ class ElasticBuffer:
         self._transport.raise_status()
 
     # ---- exchange --------------------------------------------------------------------
-    def dispatch(self, x, x_scale, topk_ids, topk_weights, *, bucket: int, expert_alignment: int, do_cpu_sync: bool) -> ReceiveResult:
+    def dispatch(self, x, x_scale, topk_ids, topk_weights, *, bucket: int, expert_alignment: int, do_cpu_sync: bool,
+                 async_finish: bool = False) -> ReceiveResult:
         self._check_live()
         if self._pending is not None:
             raise RuntimeError("Complete the previous exchange before dispatch")
@@ -290,6 +292,8 @@ class ElasticBuffer:
             raise ValueError("source input exceeds its bucket")
         if self.is_ffn and x.shape[0] != 0:
             raise ValueError("role-aware FFN ranks cannot originate tokens")
+        if async_finish and self.backend != "native":
+            raise ValueError("async_finish needs the native transport")
         self._raise_device_status()
         num_sms = self._num_sms()
         if self.is_ffn:
@@ -297,7 +301,10 @@ class ElasticBuffer:
             recv_x, recv_scale, recv_w, psum, counts, src_meta = out
             n_tokens = 0
         else:
-            self._transport.source_dispatch(x, x_scale, topk_ids, topk_weights, bucket=bucket)
+            if async_finish:
+                self.last_event = self._transport.source_dispatch(x, x_scale, topk_ids, topk_weights, bucket=bucket, async_finish=True)
+            else:
+                self._transport.source_dispatch(x, x_scale, topk_ids, topk_weights, bucket=bucket)
             recv_x, recv_scale, recv_w, psum, src_meta = self._transport.empty_receive()
             counts = [0] * self._experts_local if do_cpu_sync else []
             n_tokens = int(x.shape[0])
@@ -307,14 +314,17 @@ class ElasticBuffer:
         self._pending = handle
         return ReceiveResult(recv_x, recv_scale, recv_w, psum, list(counts), handle)
 
-    def combine(self, expert_output, handle: DispatchHandle):
+    def combine(self, expert_output, handle: DispatchHandle, *, async_finish: bool = False):
         self._check_live()
         if handle is None or handle._owner is not self._owner or handle is not self._pending:
             raise ValueError("Handle does not belong to this pending exchange")
         if tuple(expert_output.shape) != handle.recv_shape:
             raise ValueError("Expert output must match its dispatch receive shape")
         if self.is_ffn:
-            self._transport.worker_reply(expert_output)
+            if async_finish:
+                self.last_event = self._transport.worker_reply(expert_output, async_finish=True)
+            else:
+                self._transport.worker_reply(expert_output)
             combined = self._transport.empty_output()
         else:
             combined = self._transport.source_collect(handle.num_tokens)
@@ -416,8 +426,12 @@ class Buffer:
         return self.transport.comm_stream
 
     # ---- the four role calls ---------------------------------------------------------
-    def source_dispatch(self, x, ids, weights, x_scale=None, *, bucket: int, read_host_counts: bool = False) -> None:
-        """Attention: publish activations and expert ids.  No casts, no copies."""
+    def source_dispatch(self, x, ids, weights, x_scale=None, *, bucket: int, read_host_counts: bool = False, async_finish: bool = False):
+        """Attention: publish activations and expert ids.  No casts, no copies.
+
+        ``async_finish=True`` (native transport built with ``use_comm_stream=True``): the current
+        stream does not wait for the dispatch kernel; the call returns an ``EventHandle`` and the
+        inputs must not be changed until ``handle.current_stream_wait()`` (or ``synchronize()``)."""
         self._check_role("attention")
         c = self.config
         if x.ndim != 2:
@@ -430,9 +444,12 @@ class Buffer:
             raise ValueError("FP8 dispatch requires FP32 block128 scales")
         if x_scale is not None:
             self._tensor(x_scale, self._t.float32, (n, c.hidden_size // FP8_GROUP_SIZE), contiguous=False)
-        self.transport.dispatch(
-            x, x_scale, ids, weights, bucket=bucket, expert_alignment=c.expert_alignment, do_cpu_sync=read_host_counts
-        )
+        if not async_finish:
+            self.transport.dispatch(x, x_scale, ids, weights, bucket=bucket, expert_alignment=c.expert_alignment, do_cpu_sync=read_host_counts)
+            return None
+        self.transport.dispatch(x, x_scale, ids, weights, bucket=bucket, expert_alignment=c.expert_alignment, do_cpu_sync=read_host_counts,
+                                async_finish=True)
+        return self.transport.last_event
 
     def worker_receive(self, *, bucket: int, read_host_counts: bool = False) -> ReceiveResult:
         """FFN: expert-major rows, weights, device prefix sums and the receipt."""
@@ -450,11 +467,16 @@ class Buffer:
             raise RuntimeError("source_collect requires a matching dispatch")
         return self.transport.combine(self._t.empty_output(), handle)
 
-    def worker_reply(self, rows, receipt: DispatchHandle) -> None:
-        """FFN: BF16 rows of the receive shape, weighted exactly once."""
+    def worker_reply(self, rows, receipt: DispatchHandle, *, async_finish: bool = False):
+        """FFN: BF16 rows of the receive shape, weighted exactly once.  ``async_finish=True``
+        returns an ``EventHandle`` instead of making the current stream wait (see ``source_dispatch``)."""
         self._check_role("ffn")
         self._tensor(rows, self._t.bfloat16, receipt.recv_shape)
-        self.transport.combine(rows, receipt)
+        if not async_finish:
+            self.transport.combine(rows, receipt)
+            return None
+        self.transport.combine(rows, receipt, async_finish=True)
+        return self.transport.last_event
 
     def worker_serve_fused(self, weights, *, bucket: int):
         """FFN, native transport: receive, SwiGLU experts and reply of one exchange as one call.

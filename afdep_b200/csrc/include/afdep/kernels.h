@@ -65,7 +65,8 @@ struct DispatchArgs {
     const void* x;          // [T][hidden] bf16 or e4m3, contiguous
     const float* x_scale;   // FP8 only: element (t, g) at x_scale[t * ss0 + g * ss1]
     long long ss0, ss1;
-    const long long* ids;   // [T][top_k] int64
+    const long long* ids;   // [T][top_k] int64, or null with ids32
+    const int* ids32;       // [T][top_k] int32 (Buffer option topk_idx_bits=32)
     const float* weights;   // [T][top_k]
     int T;
     // 0: arrival flags are released by the CTA's flag warp behind a system-scope fence.

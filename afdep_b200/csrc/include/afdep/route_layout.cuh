@@ -36,7 +36,8 @@ struct RouteLayoutOut {
 };
 
 struct RouteLayoutJob {
-    const long long* ids;
+    const long long* ids;        // int64 ids [T][K], or null when ids32 is used
+    const int* ids32 = nullptr;  // int32 ids [T][K] (the reference's 32-bit index build, compiled.cuh:54-72)
     int T, K, E, EL, F;
     unsigned ep;                 // tag of this launch in the aggregate array
     unsigned long long* agg;     // [gridDim.x][F + E], distributed mode only
@@ -110,7 +111,7 @@ __device__ __forceinline__ bool route_layout_phase(const RouteLayoutJob& j, cons
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const int t = tb0 + u * tpb + tl;
-                idv[u] = (lane_on && t < w1) ? j.ids[(size_t)t * K + k] : -1ll;
+                idv[u] = !(lane_on && t < w1) ? -1ll : (j.ids32 != nullptr ? (long long)j.ids32[(size_t)t * K + k] : j.ids[(size_t)t * K + k]);
             }
 #pragma unroll
             for (int u = 0; u < U; ++u) {

@@ -75,6 +75,7 @@ dispatch_kernel(const RankCtx c, const AttnWs ws, const DispatchArgs a, const Di
     // ------------------------------------------------------------------ phase 1: layout
     RouteLayoutJob job;
     job.ids = a.ids;
+    job.ids32 = a.ids32;
     job.T = T;
     job.K = K;
     job.E = E;

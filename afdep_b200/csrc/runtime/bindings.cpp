@@ -229,7 +229,10 @@ public:
         TORCH_CHECK(reinterpret_cast<uintptr_t>(x.data_ptr()) % 16 == 0, "x must be 16-byte aligned");
         DispatchArgs a{};
         a.x = x.data_ptr();
-        a.ids = reinterpret_cast<const long long*>(ids.data_ptr<int64_t>());
+        if (ids.scalar_type() == torch::kInt32)
+            a.ids32 = ids.data_ptr<int>();
+        else
+            a.ids = reinterpret_cast<const long long*>(ids.data_ptr<int64_t>());
         a.weights = weights.data_ptr<float>();
         a.T = T;
         static const int flag_mode = std::getenv("AFDEP_FLAG_MODE") ? std::atoi(std::getenv("AFDEP_FLAG_MODE")) : 0;
@@ -961,7 +964,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         d["cuda_compiled"] = CUDART_VERSION;
         d["cuda_runtime"] = runtime;
         d["cuda_driver"] = driver;
-        d["topk_index_dtype"] = "int64";
+        d["topk_index_dtype"] = "int64 or int32 (Buffer option topk_idx_bits)";
         d["max_ranks"] = afdep::kMaxRanks;
         d["trace_ctas"] = afdep::kTraceCtas;
         d["stream_memops"] = true;

@@ -20,6 +20,29 @@ def _env_int(name: str, default: int) -> int:
     return int(value) if value else default
 
 
+class EventHandle:
+    """What an asynchronous role call hands back: the event that marks the end of the call's
+    kernels on the communication stream, plus references that keep the call's tensors alive until
+    then.  Counterpart of the reference's EventHandle (csrc/utils/event.hpp:10-42)."""
+
+    def __init__(self, torch_module, event, keep_alive) -> None:
+        self._torch, self.event, self._keep_alive = torch_module, event, keep_alive
+
+    def current_stream_wait(self) -> None:
+        """Make the current stream wait for the call (a no-op when the call ran on the current stream)."""
+        if self.event is not None:
+            self._torch.cuda.current_stream().wait_event(self.event)
+        self._keep_alive = ()
+
+    def synchronize(self) -> None:
+        if self.event is not None:
+            self.event.synchronize()
+        self._keep_alive = ()
+
+    def query(self) -> bool:
+        return True if self.event is None else bool(self.event.query())
+
+
 class NativeTransport:
     def __init__(self, *, control, group, config: Config, num_sms: int, options: dict) -> None:
         import torch
@@ -31,7 +54,10 @@ class NativeTransport:
         self._torch, self._control, self.config = torch, control, config
         self._native = load_native()
         self.device = torch.cuda.current_device()
-        self.topk_idx_dtype = torch.int64
+        bits = int(options.get("topk_idx_bits", os.environ.get("AFDEP_TOPK_IDX_BITS", "64")))
+        if bits not in (32, 64):
+            raise ValueError("topk_idx_bits must be 32 or 64")
+        self.topk_idx_dtype = torch.int64 if bits == 64 else torch.int32
         self.payload_dtype = torch.float8_e4m3fn if config.is_fp8 else torch.bfloat16
         self.float32, self.bfloat16 = torch.float32, torch.bfloat16
         self._failed: str | None = None
@@ -149,12 +175,15 @@ class NativeTransport:
         finally:
             self._torch.cuda.nvtx.range_pop()
 
-    def _on_comm_stream(self, fn, *tensors):
+    def _on_comm_stream(self, fn, *tensors, async_finish: bool = False):
         """Run ``fn`` on the communication stream, after everything queued on the current stream,
         and make the current stream wait for it.  Tensors used by ``fn`` are recorded on the
-        communication stream so the caching allocator does not recycle them early."""
+        communication stream so the caching allocator does not recycle them early.  With
+        ``async_finish`` the current stream does *not* wait: the caller gets ``(result, EventHandle)``
+        and joins later with ``handle.current_stream_wait()``."""
         if self._comm_stream is None:
-            return fn()
+            out = fn()
+            return (out, EventHandle(self._torch, None, ())) if async_finish else out
         torch = self._torch
         current = torch.cuda.current_stream(self.device)
         self._comm_stream.wait_stream(current)
@@ -163,6 +192,10 @@ class NativeTransport:
         for t in tensors:
             if t is not None and t.numel():
                 t.record_stream(self._comm_stream)
+        if async_finish:
+            done = torch.cuda.Event()
+            done.record(self._comm_stream)
+            return out, EventHandle(torch, done, tuple(t for t in tensors if t is not None))
         current.wait_stream(self._comm_stream)
         # results were allocated while the communication stream was current but are consumed on
         # the caller's stream: tell the allocator, or a freed block could be reused too early
@@ -244,8 +277,12 @@ class NativeTransport:
     def empty_output(self):
         return self._empties()["out"]
 
-    def source_dispatch(self, x, x_scale, ids, weights, *, bucket: int) -> None:
-        self._ranged("source_dispatch", lambda: self._on_comm_stream(lambda: self._nb.source_dispatch(x, x_scale, ids, weights), x, x_scale, ids, weights))
+    def source_dispatch(self, x, x_scale, ids, weights, *, bucket: int, async_finish: bool = False):
+        out = self._ranged(
+            "source_dispatch",
+            lambda: self._on_comm_stream(lambda: self._nb.source_dispatch(x, x_scale, ids, weights), x, x_scale, ids, weights, async_finish=async_finish),
+        )
+        return out[1] if async_finish else None
 
     def source_collect(self, num_tokens: int):
         return self._ranged("source_collect", lambda: self._on_comm_stream(lambda: self._nb.source_collect(num_tokens)))
@@ -274,8 +311,9 @@ class NativeTransport:
             lambda: self._on_comm_stream(lambda: self._nb.worker_mlp_fused(tensors[0], tensors[1], tensors[2], tensors[3], rows), *tensors),
         )
 
-    def worker_reply(self, rows) -> None:
-        self._ranged("worker_reply", lambda: self._on_comm_stream(lambda: self._nb.worker_reply(rows), rows))
+    def worker_reply(self, rows, *, async_finish: bool = False):
+        out = self._ranged("worker_reply", lambda: self._on_comm_stream(lambda: self._nb.worker_reply(rows), rows, async_finish=async_finish))
+        return out[1] if async_finish else None
 
     def close(self) -> None:
         torch = self._torch

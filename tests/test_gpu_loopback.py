@@ -361,6 +361,57 @@ def test_dispatch_grid_is_co_resident_or_refused():
         world.close()
 
 
+def test_int32_expert_ids():
+    """The 32-bit index build of the reference (EP_NUM_TOPK_IDX_BITS=32) as a Buffer option."""
+    cfg = Config(48, 512, 16, 4, 2, 2, expert_alignment=8)
+    world = make_world(cfg, topk_idx_bits=32)
+    try:
+        assert world.attention[0].topk_idx_dtype == torch.int32
+        batches = [synthetic.exact_batch(cfg, 48 - 5 * a, a, 1) for a in range(2)]
+        dev = [(x.cuda(), ids.to(torch.int32).cuda(), w.cuda(), None) for x, ids, w, _ in batches]
+
+        def expert(i, rec):
+            return oracle.synthetic_expert_rows(cfg, i, rec.recv_x, rec.recv_scale, rec.recv_topk_weights, rec.recv_count_psum)
+
+        outs, _ = world.exchange(dev, expert)
+        torch.cuda.synchronize()
+        for a, out in enumerate(outs):
+            assert torch.equal(out.cpu().float(), oracle.expected_combine(cfg, oracle.SourceBatch(*batches[a])).float())
+        with pytest.raises(ValueError):
+            world.attention[0].source_dispatch(dev[0][0], batches[0][1].cuda(), dev[0][2], None, bucket=48)     # int64 ids into a 32-bit Buffer
+        for b in world.buffers:
+            b.check()
+    finally:
+        world.close()
+
+
+def test_async_finish_hands_back_an_event():
+    """Role calls on the dedicated communication stream that do not make the caller's stream wait:
+    the caller joins through the EventHandle (the reference's async / EventHandle mode,
+    csrc/utils/event.hpp:10-42)."""
+    cfg = Config(32, 512, 8, 2, 1, 1, expert_alignment=8)
+    world = make_world(cfg, use_comm_stream=True)
+    try:
+        att, ffn = world.attention[0], world.ffn[0]
+        batch = synthetic.exact_batch(cfg, 32, 0, 2)
+        x, ids, w, _ = to_dev(batch)
+        handle = att.source_dispatch(x, ids, w, None, bucket=32, async_finish=True)
+        assert handle is not None and hasattr(handle, "current_stream_wait")
+        handle.current_stream_wait()
+        rec = ffn.worker_receive(bucket=32)
+        rows = oracle.synthetic_expert_rows(cfg, 0, rec.recv_x, rec.recv_scale, rec.recv_topk_weights, rec.recv_count_psum)
+        done = ffn.worker_reply(rows, rec.receipt, async_finish=True)
+        done.current_stream_wait()
+        out = att.source_collect()
+        torch.cuda.synchronize()
+        assert done.query()
+        assert torch.equal(out.cpu().float(), oracle.expected_combine(cfg, oracle.SourceBatch(*batch)).float())
+        for b in world.buffers:
+            b.check()
+    finally:
+        world.close()
+
+
 def test_dedicated_comm_stream_option():
     """Exchange kernels on a separate high-priority stream, ordered with events."""
     cfg = Config(32, 512, 8, 2, 2, 2, expert_alignment=8)
