@@ -75,7 +75,9 @@ class NativeTransport:
         if "gpu_timeout_s" in options:
             timeout_s = float(options["gpu_timeout_s"])
         sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
-        collect_sms = int(options.get("collect_sms", _env_int("AFDEP_COLLECT_SMS", 0))) or min(sm_count, 2 * num_sms)
+        # the collect kernel pulls one token per warp at a time: every SM takes part, as the reference's
+        # reduce epilogue does (csrc/kernels/elastic/combine.hpp:248-287), unless the caller caps it
+        collect_sms = int(options.get("collect_sms", _env_int("AFDEP_COLLECT_SMS", 0))) or sm_count
         ffn_sms = int(options.get("ffn_sms", _env_int("AFDEP_FFN_SMS", 0))) or sm_count
         bounds = bool(int(os.environ.get("AFDEP_BOUNDS_CHECK", "1")))
 
