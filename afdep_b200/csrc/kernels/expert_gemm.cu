@@ -194,6 +194,8 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         // ------------------------------------------------------------------ producer
         int stage = 0, tcount = 0;
         unsigned phase = 0;
+        int next_rows[BM / 32];
+        bool have_next = false;
         for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
             int e, row0, col0;
             decode(w, e, row0, col0);
@@ -203,7 +205,7 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 bool ok = true;
                 if (lane == 0) {
                     ok = wait_bar(&ctrl->rows_empty[buf], ((tcount >> 1) & 1u) ^ 1u, failed, p.budget);
-                    if (ok && fused) {
+                    if (ok && fused && !have_next) {
                         // every row of the tile has been indexed, i.e. all of its records have landed
                         const unsigned* cnt = fr.tile_cnt + (row0 >> 7);
                         const long long t0 = clock64();
@@ -223,11 +225,37 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 #pragma unroll
                 for (int j = 0; j < BM / 32; ++j) {
                     const int r = lane + 32 * j;
-                    ctrl->tile_rows[buf][r] = (r < valid) ? __ldcg(p.row_rec + row0 + r) : -1;
+                    if (!have_next) next_rows[j] = (r < valid) ? __ldcg(p.row_rec + row0 + r) : -1;
+                    ctrl->tile_rows[buf][r] = next_rows[j];
                 }
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(&ctrl->rows_full[buf]);
                 ++tcount;
+                // The row indices of this CTA's next tile are fetched now, so that their latency
+                // passes while this tile's weights stream instead of holding up the next tile's
+                // first loads.  In the fused form only a tile whose records have all been indexed
+                // already is fetched ahead; any other waits for its counter when its turn comes.
+                have_next = false;
+                const int wn = w + (int)gridDim.x;
+                if (wn < total_work) {
+                    int en, rown, coln;
+                    decode(wn, en, rown, coln);
+                    const int validn = min(BM, p.ends[en] - rown);
+                    bool ready = true;
+                    if (fused) {
+                        if (lane == 0) ready = ptx::ld_acquire_gpu(fr.tile_cnt + (rown >> 7)) >= (unsigned)validn;
+                        ready = __shfl_sync(ptx::kFullMask, ready, 0);
+                        __syncwarp();
+                    }
+                    if (ready) {
+#pragma unroll
+                        for (int j = 0; j < BM / 32; ++j) {
+                            const int r = lane + 32 * j;
+                            next_rows[j] = (r < validn) ? __ldcg(p.row_rec + rown + r) : -1;
+                        }
+                        have_next = true;
+                    }
+                }
             }
             if (lane == 0) {
                 for (int kb = 0; kb < num_kb; ++kb) {
@@ -366,11 +394,15 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             int e, row0, col0;
             decode(w, e, row0, col0);
             int rec_a[8], rec_s[4];
+            const unsigned char* src_a[8];
             if (kGather) {
                 const int buf = tcount & 1;
                 if (!wait_bar_warp(&ctrl->rows_full[buf], (tcount >> 1) & 1u, failed, p.budget)) break;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) rec_a[i] = ctrl->tile_rows[buf][i * 16 + (ft >> 3)];
+                for (int i = 0; i < 8; ++i) {
+                    rec_a[i] = ctrl->tile_rows[buf][i * 16 + (ft >> 3)];
+                    src_a[i] = p.a_rows + (size_t)(rec_a[i] >= 0 ? rec_a[i] : 0) * p.a_pitch + (ft & 7) * 16;
+                }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) rec_s[j] = ctrl->tile_rows[buf][32 * j + lane];
                 __syncwarp();
@@ -381,15 +413,25 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             // Scales of one group (four K blocks): four rows per lane for A, two 128-column blocks for W.
             // They are fetched one group ahead, so their latency never holds up the row gathering.
             float sa[4][4], sb[2][4];
+            const int kgroups = p.K / 128;
+            const bool from_records = kGather && p.a_scale == nullptr;
+            const float4* rec_scale[4];                  // gathered rows: the scales sit in the record, behind the payload
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                rec_scale[j] = (from_records && rec_s[j] >= 0)
+                                   ? reinterpret_cast<const float4*>(p.a_rows + (size_t)rec_s[j] * p.a_pitch + p.a_scale_off)
+                                   : nullptr;
+            const float* w_scale0 = kMx ? p.w_scale + ((size_t)e * (p.N / 128) + col0 / 128) * kgroups : nullptr;
+            const bool w_second = col0 + 128 < p.N;      // the tile's second 128-column block exists
+            // groups of four scales are 16-byte aligned
+            const bool w_vec = (kgroups & 3) == 0 && (reinterpret_cast<uintptr_t>(p.w_scale) & 15) == 0;
             auto fetch_scales = [&](int kb0) {
-                const int kgroups = p.K / 128;
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int r = 32 * j + lane;
-                    if (kGather && p.a_scale == nullptr) {
+                    if (from_records) {
                         float4 v = make_float4(1.f, 1.f, 1.f, 1.f);
-                        if (rec_s[j] >= 0)
-                            v = __ldcg(reinterpret_cast<const float4*>(p.a_rows + (size_t)rec_s[j] * p.a_pitch + p.a_scale_off) + (kb0 >> 2));
+                        if (rec_scale[j] != nullptr) v = __ldcg(rec_scale[j] + (kb0 >> 2));
                         sa[j][0] = v.x;
                         sa[j][1] = v.y;
                         sa[j][2] = v.z;
@@ -404,64 +446,102 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 }
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    const int nb = col0 / 128 + h;
+                    const float* src = w_scale0 + (size_t)h * kgroups + kb0;
+                    if (h == 1 && !w_second) {
 #pragma unroll
-                    for (int b = 0; b < 4; ++b)
-                        sb[h][b] = (kb0 + b < num_kb && nb * 128 < p.N) ? __ldg(p.w_scale + ((size_t)e * (p.N / 128) + nb) * kgroups + kb0 + b) : 1.f;
+                        for (int b = 0; b < 4; ++b) sb[h][b] = 1.f;
+                    } else if (w_vec) {
+                        const float4 v = __ldg(reinterpret_cast<const float4*>(src));
+                        sb[h][0] = v.x;
+                        sb[h][1] = v.y;
+                        sb[h][2] = v.z;
+                        sb[h][3] = v.w;
+                    } else {
+#pragma unroll
+                        for (int b = 0; b < 4; ++b) sb[h][b] = (kb0 + b < num_kb) ? __ldg(src + b) : 1.f;
+                    }
                 }
+            };
+            // One scale group (four K blocks) takes four steps: pack the rows' scales into exponent
+            // bytes; pack the columns' and start fetching the group after; store the bytes to TMEM once
+            // the slot is free; wait for the stores and publish the slot.  The steps are spread over
+            // the stages of the group BEFORE, one after each stage's copies have gone out, so that no
+            // stage's copies start late by a whole group's work: a ring of four stages would delay the
+            // same stage every time round, and the MMAs would wait for it every time.
+            uint32_t wa[4], wb[2];
+            auto pack_rows = [&](int kb0) {
+                const bool whole = kb0 + 4 <= num_kb;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    uint32_t word = 0;
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) word |= ((whole || kb0 + b < num_kb) ? tc::ue8m0_of_pow2(sa[j][b]) : 127u) << (8 * b);
+                    wa[j] = word;
+                }
+            };
+            auto pack_cols = [&](int kb0) {                  // and start on the group after: both arrays are free now
+                const bool whole = kb0 + 4 <= num_kb;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t word = 0;
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) word |= ((whole || kb0 + b < num_kb) ? tc::ue8m0_of_pow2(sb[h][b]) : 127u) << (8 * b);
+                    wb[h] = word;
+                }
+                if (kb0 + 4 < num_kb) fetch_scales(kb0 + 4);
+            };
+            auto store = [&]() -> bool {
+                const unsigned slot = group % kSfSlots;
+                if (!wait_bar_warp(&ctrl->sf_empty[slot], ((group / kSfSlots) & 1u) ^ 1u, failed, p.budget)) return false;
+                tc::fence_after_sync();
+                const uint32_t dst = tmem + lane_base + (uint32_t)(kSfBase + slot * kSfSlotCols);
+                uint32_t wide[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) wide[j] = wb[j >> 2];
+                tc::tmem_st4(dst, wa[0], wa[1], wa[2], wa[3]);
+                tc::tmem_st8(dst + 4, wide);
+                return true;
+            };
+            auto publish = [&]() {
+                tc::tmem_st_wait();
+                tc::fence_before_sync();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(&ctrl->sf_full[group % kSfSlots]);
+                ++group;
             };
             if (kMx) fetch_scales(0);
             bool ok = true;
-            for (int kb = 0; kb < num_kb; ++kb) {
-                if (kMx && (kb & 3) == 0) {
-                    // exponent bytes of K blocks kb .. kb+3: A's rows (4 columns), W's columns (8 columns)
-                    const unsigned slot = group % kSfSlots;
-                    uint32_t wa[4], wb[8];
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        uint32_t word = 0;
-#pragma unroll
-                        for (int b = 0; b < 4; ++b) word |= ((kb + b < num_kb) ? tc::ue8m0_of_pow2(sa[j][b]) : 127u) << (8 * b);
-                        wa[j] = word;
-                    }
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        uint32_t word = 0;
-#pragma unroll
-                        for (int b = 0; b < 4; ++b) word |= ((kb + b < num_kb) ? tc::ue8m0_of_pow2(sb[h][b]) : 127u) << (8 * b);
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) wb[4 * h + j] = word;
-                    }
-                    if (kb + 4 < num_kb) fetch_scales(kb + 4);      // in flight while the next four stages are fed
-                    if (!wait_bar_warp(&ctrl->sf_empty[slot], ((group / kSfSlots) & 1u) ^ 1u, failed, p.budget)) {
-                        ok = false;
-                        break;
-                    }
-                    tc::fence_after_sync();
-                    const uint32_t dst = tmem + lane_base + (uint32_t)(kSfBase + slot * kSfSlotCols);
-                    tc::tmem_st4(dst, wa[0], wa[1], wa[2], wa[3]);
-                    tc::tmem_st8(dst + 4, wb);
-                    tc::tmem_st_wait();
-                    tc::fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(&ctrl->sf_full[slot]);
-                    ++group;
-                }
+            for (int kb = 0; kb < num_kb && ok; ++kb) {
                 if (kGather) {
                     if (!wait_bar_warp(&ctrl->empty[stage], phase ^ 1u, failed, p.budget)) {
                         ok = false;
                         break;
                     }
-                    unsigned char* sa = smem + stage * kStageBytes;
+                    unsigned char* dst_a = smem + stage * kStageBytes;
                     const int chunk = ft & 7;
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const int r = i * 16 + (ft >> 3);
-                        const int rec = rec_a[i];
-                        const unsigned char* src = p.a_rows + (size_t)(rec >= 0 ? rec : 0) * p.a_pitch + (size_t)kb * 128 + chunk * 16;
-                        tc::cp_async16(sa + r * 128 + ((chunk ^ (r & 7)) << 4), src, rec >= 0 ? 16u : 0u);
+                        tc::cp_async16(dst_a + r * 128 + ((chunk ^ (r & 7)) << 4), src_a[i] + (size_t)kb * 128, rec_a[i] >= 0 ? 16u : 0u);
                     }
                     tc::cp_async_arrive(&ctrl->full[stage]);
+                }
+                if (kMx) {
+                    const int g = kb >> 2, step = kb & 3, next = 4 * g + 4;
+                    if (kb == 0) {                       // the tile's first group, all at once
+                        pack_rows(0);
+                        pack_cols(0);
+                        ok = store();
+                        if (ok) publish();
+                    } else if (next < num_kb) {          // group g + 1 during group g
+                        if (step == 0) pack_rows(next);
+                        if (step == 1) {
+                            if (g == 0) pack_rows(next);     // stage 0 was busy with the first group
+                            pack_cols(next);
+                        }
+                        if (step == 2) ok = store();
+                        if (step == 3) publish();
+                    }
                 }
                 if (++stage == kStages) {
                     stage = 0;
