@@ -19,7 +19,7 @@ directions (one record per token and destination FFN rank out, one BF16 row back
 the step time; ``us_per_exchange`` and ``per_rank_GBs`` are the per-rank figures.  ``phases``
 are kernel durations read from device time stamps of one traced graph replay.  The ``e2e``
 entry repeats the measurement with, inside the timed region and every step, the host->device
-copy of the step's inputs from pinned memory and a device->host read of a checksum of the
+copy of the step's inputs from pinned memory (one block per rank, one copy) and a device->host read of a checksum of the
 result: ``serial`` issues the copy on the compute stream, the headline e2e ``value`` stages
 step n+1's copy on a second stream while step n runs.  With ``--gpus 8`` the line also carries
 sub-results for the 8-GPU configurations 3, 4 and 5 under ``extra``.
@@ -273,8 +273,28 @@ def run_config(env: Env, name: str, *, steps: int, warmup: int, tokens: int = 0,
         s = {"buf": buf}
         if buf.role == "attention":
             x, ids, w, scale = synthetic.random_batch(cfg, T, seed=1000 + buf.role_rank, zipf_s=spec["zipf"], pow2_scales=pow2)
-            s["host"] = [t.pin_memory() if t is not None else None for t in (x, ids, w, scale)]
-            s["dev"] = [[t.to(dev) if t is not None else None for t in s["host"]] for _ in range(2)]
+            # One pinned block holds a step's inputs back to back (256-byte aligned), and each of the
+            # two device input sets is one block of the same shape: a step's inputs cross PCIe as one
+            # copy instead of one per tensor.
+            parts, offset = [], 0
+            for t in (x, ids, w, scale):
+                if t is None:
+                    parts.append(None)
+                    continue
+                nbytes = t.numel() * t.element_size()
+                parts.append((offset, nbytes, t.dtype, tuple(t.shape)))
+                offset = (offset + nbytes + 255) // 256 * 256
+
+            def views(block):
+                return [None if q is None else block[q[0]:q[0] + q[1]].view(q[2]).view(q[3]) for q in parts]
+
+            s["host_block"] = torch.empty(offset, dtype=torch.uint8).pin_memory()
+            s["host"] = views(s["host_block"])
+            for v, t in zip(s["host"], (x, ids, w, scale)):
+                if t is not None:
+                    v.copy_(t)
+            s["dev_block"] = [s["host_block"].to(dev) for _ in range(2)]
+            s["dev"] = [views(b) for b in s["dev_block"]]
             s["ids_cpu"] = ids
         elif experts_on:
             from afdep_b200.models.moe_layer import ExpertWeights
@@ -495,16 +515,14 @@ def run_config(env: Env, name: str, *, steps: int, warmup: int, tokens: int = 0,
     e2e = None
     if with_e2e:
         copy_stream = torch.cuda.Stream()
-        h2d = sum(sum(t.numel() * t.element_size() for t in s["host"] if t is not None) for s in state if "host" in s)
+        h2d = sum(s["host_block"].numel() for s in state if "host" in s)
         h2d = sum(env.gather(h2d))
 
         def copy_inputs(which, stream):
             with torch.cuda.stream(stream):
                 for s in state:
                     if "host" in s:
-                        for d, h in zip(s["dev"][which], s["host"]):
-                            if d is not None:
-                                d.copy_(h, non_blocking=True)
+                        s["dev_block"][which].copy_(s["host_block"], non_blocking=True)
 
         def e2e_serial(count):
             cur = torch.cuda.current_stream()
