@@ -124,6 +124,7 @@ class ElasticBuffer:
         ffn_ranks: int | None = None,
         expert_alignment: int = 128,
         backend: str = "native",
+        scale_format: str = "fp32",
         _control=None,
         _transport_options: dict | None = None,
     ) -> None:
@@ -156,6 +157,7 @@ class ElasticBuffer:
             "ffn_ranks": ffn_ranks,
             "alignment": expert_alignment,
             "backend": backend,
+            "scale_format": scale_format,
         }
         error, probe = None, {}
         try:
@@ -198,6 +200,7 @@ class ElasticBuffer:
             cpu_timeout_s=cpu_timeout_s,
             gpu_timeout_s=gpu_timeout_s,
             role_aware=role_aware,
+            scale_format=scale_format,
         )
         self._resolved_num_sms = self._config.resolved_num_sms(min_sms) if min_sms else num_sms
         self._transport = _make_transport(
@@ -227,6 +230,8 @@ class ElasticBuffer:
                 raise ValueError(f"{key} must be a nonnegative int32 integer")
         if type(s["hybrid"]) is not bool or type(s["fp8"]) is not bool or type(s["role_aware"]) is not bool:
             raise ValueError("hybrid, FP8 and role_aware settings must be booleans")
+        if s["scale_format"] not in ("fp32", "ue8m0x4") or (s["scale_format"] != "fp32" and not s["fp8"]):
+            raise ValueError("scale_format must be 'fp32', or 'ue8m0x4' with FP8 dispatch")
         ffn = s["ffn_ranks"]
         if ffn is not None and (type(ffn) is not int or not 0 < ffn < self.world_size):
             raise ValueError("ffn_ranks must leave positive FFN and source ranks")
@@ -388,6 +393,7 @@ class Buffer:
             cpu_timeout_s=config.cpu_timeout_s,
             gpu_timeout_s=config.gpu_timeout_s,
             use_fp8_dispatch=config.payload == "fp8",
+            scale_format=config.scale_format,
             num_sms=config.num_sms,
             num_qps=config.num_qps,
             role_aware=config.role_aware,
@@ -443,7 +449,10 @@ class Buffer:
         if (x_scale is not None) != (c.payload == "fp8"):
             raise ValueError("FP8 dispatch requires FP32 block128 scales")
         if x_scale is not None:
-            self._tensor(x_scale, self._t.float32, (n, c.hidden_size // FP8_GROUP_SIZE), contiguous=False)
+            if c.scale_packed:      # exponent bytes, four to an int32 word
+                self._tensor(x_scale, self._t.scale_dtype, (n, c.scale_groups), contiguous=False)
+            else:
+                self._tensor(x_scale, self._t.float32, (n, c.hidden_size // FP8_GROUP_SIZE), contiguous=False)
         if not async_finish:
             self.transport.dispatch(x, x_scale, ids, weights, bucket=bucket, expert_alignment=c.expert_alignment, do_cpu_sync=read_host_counts)
             return None

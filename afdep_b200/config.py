@@ -80,6 +80,12 @@ class Config:
     cpu_timeout_s: int = 120
     gpu_timeout_s: int = 120
     role_aware: bool = True
+    # Not in the reference's dataclass: the form of an FP8 payload's scales.  "fp32" is the
+    # reference's public contract (one fp32 scale per 128 channels).  "ue8m0x4" carries the scales
+    # as exponent bytes packed four to an int32 word, the element the reference's native layer
+    # also admits (deep_ep/include/deep_ep/common/compiled.cuh:74-77) and the one Blackwell's
+    # block-scaled MMA consumes; the exchange moves the words untouched.
+    scale_format: Literal["fp32", "ue8m0x4"] = "fp32"
 
     def __post_init__(self) -> None:
         for name in _POSITIVE:
@@ -103,6 +109,10 @@ class Config:
             raise ValueError("top_k must be <=32 and <=num_experts")
         if self.payload not in ("bf16", "fp8"):
             raise ValueError("payload must be 'bf16' or 'fp8'")
+        if self.scale_format not in ("fp32", "ue8m0x4"):
+            raise ValueError("scale_format must be 'fp32' or 'ue8m0x4'")
+        if self.scale_format != "fp32" and self.payload != "fp8":
+            raise ValueError("scale_format applies to FP8 payloads only")
         if (
             self.world_size > MAX_RANKS
             or self.logical_experts > MAX_LOGICAL_EXPERTS
@@ -137,8 +147,14 @@ class Config:
 
     @property
     def scale_groups(self) -> int:
-        """fp32 scales per row of an FP8 payload (one per 128 channels)."""
-        return self.hidden_size // FP8_GROUP_SIZE
+        """4-byte scale elements per row of an FP8 payload: one fp32 scale per 128 channels, or
+        one int32 word per four of them when the scales travel as packed exponent bytes."""
+        groups = self.hidden_size // FP8_GROUP_SIZE
+        return (groups + 3) // 4 if self.scale_packed else groups
+
+    @property
+    def scale_packed(self) -> bool:
+        return self.scale_format == "ue8m0x4"
 
     def receive_rows(self, bucket: int) -> int:
         """Upper bound on expert-major rows an FFN rank can receive for ``bucket``.

@@ -57,8 +57,11 @@ struct Geometry {
 
 AFDEP_HD int cnt_stride(const Geometry& g) { return g.experts_local + 4; }
 
+// `scale_packs`: 4-byte scale words per FP8 row.  0 means one fp32 scale per 128 channels; a caller
+// whose scales are exponent bytes packed four to a word (UE8M0x4) passes the number of words.  The
+// exchange moves the words as they are.
 inline Geometry make_geometry(int ffn, int attn, int hidden, int top_k, int num_experts, int capacity, int fp8,
-                              int alignment, size_t aux_bytes) {
+                              int alignment, size_t aux_bytes, int scale_packs = 0) {
     Geometry g{};
     g.world = ffn + attn;
     g.ffn = ffn;
@@ -70,7 +73,7 @@ inline Geometry make_geometry(int ffn, int attn, int hidden, int top_k, int num_
     g.capacity = capacity;
     g.fp8 = fp8;
     g.alignment = alignment;
-    g.scale_groups = hidden / 128;
+    g.scale_groups = scale_packs > 0 ? scale_packs : hidden / 128;
     g.payload_bytes = hidden * (fp8 ? 1 : 2);
     g.scale_bytes = fp8 ? (int)align_sz((size_t)g.scale_groups * 4, 16) : 0;
     g.meta_bytes = (int)align_sz((size_t)top_k * 12 + 4, 16);

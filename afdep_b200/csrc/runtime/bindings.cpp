@@ -112,14 +112,15 @@ class NativeBuffer {
 public:
     NativeBuffer(int rank, int ffn, int attn, int hidden, int top_k, int num_experts, int capacity, bool fp8,
                  int alignment, int num_sms, int collect_sms, int ffn_sms, double gpu_timeout_s,
-                 int64_t aux_bytes, const std::string& heap_mode, bool bounds_check, int p2p_inflight)
+                 int64_t aux_bytes, const std::string& heap_mode, bool bounds_check, int p2p_inflight, int scale_packs)
         : rank_(rank), num_sms_(num_sms), collect_sms_(collect_sms), ffn_sms_(ffn_sms), p2p_inflight_(p2p_inflight) {
         TORCH_CHECK(p2p_inflight >= 1 && p2p_inflight <= 64, "p2p_inflight must be between 1 and 64");
         TORCH_CHECK(ffn + attn <= kMaxRanks, "the native transport supports at most ", kMaxRanks, " ranks");
         TORCH_CHECK(num_experts <= kMaxExperts && num_experts / ffn <= kMaxExpertsLocal, "too many experts");
         TORCH_CHECK(top_k <= kMaxTopK, "top_k too large");
         rt_check(cudaGetDevice(&device_), "cudaGetDevice");
-        geo_ = make_geometry(ffn, attn, hidden, top_k, num_experts, capacity, fp8 ? 1 : 0, alignment, (size_t)aux_bytes);
+        TORCH_CHECK(scale_packs >= 0 && scale_packs <= hidden / 128, "scale_packs must be between 0 and hidden / 128");
+        geo_ = make_geometry(ffn, attn, hidden, top_k, num_experts, capacity, fp8 ? 1 : 0, alignment, (size_t)aux_bytes, scale_packs);
         is_ffn_ = rank < ffn;
         role_rank_ = is_ffn_ ? rank : rank - ffn;
         const size_t bytes = is_ffn_ ? geo_.f_bytes : geo_.a_bytes;
@@ -361,6 +362,8 @@ public:
                                const torch::Tensor& w_down, const c10::optional<torch::Tensor>& w_down_scale, int64_t rows_bound) {
         live();
         TORCH_CHECK(is_ffn_, "worker_mlp_fused runs on FFN ranks");
+        TORCH_CHECK(!geo_.fp8 || geo_.scale_groups == geo_.hidden / 128,
+                    "the fused expert path reads fp32 scales out of the records; packed scale words take the separate calls");
         const int EL = geo_.experts_local, H = geo_.hidden;
         const bool fp8 = geo_.fp8 != 0;
         const auto wdt = fp8 ? torch::kFloat8_e4m3fn : torch::kBFloat16;
@@ -972,8 +975,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     });
     // Heap layout and launch shapes as plain numbers, for checks that need no GPU: offsets,
     // alignments and shared-memory budgets are pure functions of the configuration.
-    m.def("geometry", [](int ffn, int attn, int hidden, int top_k, int num_experts, int capacity, bool fp8, int alignment, int64_t aux_bytes) {
-        const afdep::Geometry g = afdep::make_geometry(ffn, attn, hidden, top_k, num_experts, capacity, fp8 ? 1 : 0, alignment, (size_t)aux_bytes);
+    m.def("geometry", [](int ffn, int attn, int hidden, int top_k, int num_experts, int capacity, bool fp8, int alignment, int64_t aux_bytes,
+                         int scale_packs) {
+        const afdep::Geometry g = afdep::make_geometry(ffn, attn, hidden, top_k, num_experts, capacity, fp8 ? 1 : 0, alignment, (size_t)aux_bytes, scale_packs);
         py::dict d;
         d["payload_bytes"] = g.payload_bytes;
         d["scale_bytes"] = g.scale_bytes;
@@ -994,7 +998,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         d["a_reply_flag"] = (int64_t)g.a_reply_flag;
         d["a_bytes"] = (int64_t)g.a_bytes;
         return d;
-    });
+    },
+          py::arg("ffn"), py::arg("attn"), py::arg("hidden"), py::arg("top_k"), py::arg("num_experts"), py::arg("capacity"), py::arg("fp8"),
+          py::arg("alignment"), py::arg("aux_bytes"), py::arg("scale_packs") = 0);
     m.def("launch_shapes", [](int ffn, int attn, int hidden, int top_k, int num_experts, int capacity, bool fp8, int alignment, int tokens,
                               int num_sms, int collect_sms, int ffn_sms, int max_smem) {
         const afdep::Geometry g = afdep::make_geometry(ffn, attn, hidden, top_k, num_experts, capacity, fp8 ? 1 : 0, alignment, 0);
@@ -1022,10 +1028,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     m.def("quantize_rows_fp8", &afdep::quantize_rows_fp8, py::arg("x"), py::arg("limit") = py::none(), py::arg("pow2") = false);
     m.def("route_layout", &afdep::route_layout, py::arg("ids"), py::arg("num_experts"), py::arg("ffn_ranks"));
     py::class_<NativeBuffer>(m, "NativeBuffer")
-        .def(py::init<int, int, int, int, int, int, int, bool, int, int, int, int, double, int64_t, const std::string&, bool, int>(),
+        .def(py::init<int, int, int, int, int, int, int, bool, int, int, int, int, double, int64_t, const std::string&, bool, int, int>(),
              py::arg("rank"), py::arg("ffn"), py::arg("attn"), py::arg("hidden"), py::arg("top_k"), py::arg("num_experts"),
              py::arg("capacity"), py::arg("fp8"), py::arg("alignment"), py::arg("num_sms"), py::arg("collect_sms"),
-             py::arg("ffn_sms"), py::arg("gpu_timeout_s"), py::arg("aux_bytes"), py::arg("heap_mode"), py::arg("bounds_check"), py::arg("p2p_inflight") = 4)
+             py::arg("ffn_sms"), py::arg("gpu_timeout_s"), py::arg("aux_bytes"), py::arg("heap_mode"), py::arg("bounds_check"), py::arg("p2p_inflight") = 4,
+             py::arg("scale_packs") = 0)
         .def("heap_bytes", &NativeBuffer::heap_bytes)
         .def("mapped_bytes", &NativeBuffer::mapped_bytes)
         .def("local_ptr", &NativeBuffer::local_ptr)

@@ -90,6 +90,16 @@ class ExpertWeights:
         return ExpertWeights(q, scale, down_w, I, mode)
 
 
+def _fp32_scales(scale, hidden: int):
+    """Received scales as fp32 [rows, hidden / 128]: packed exponent bytes (int32 words, from a
+    Buffer with ``scale_format="ue8m0x4"``) are expanded, fp32 scales pass through."""
+    if scale is not None and scale.dtype == torch.int32:
+        from ..utils.scales import unpack_ue8m0x4
+
+        return unpack_ue8m0x4(scale, hidden // 128)
+    return scale
+
+
 def run_experts(received: ReceiveResult, weights: ExpertWeights, alignment: int, *, scratch: dict | None = None) -> torch.Tensor:
     """BF16 rows for ``worker_reply``: SwiGLU MLP of every received row, times its routing weight."""
     x, ends = received.recv_x, received.recv_count_psum
@@ -99,7 +109,7 @@ def run_experts(received: ReceiveResult, weights: ExpertWeights, alignment: int,
         # BF16 dispatch into FP8 experts: quantise the live rows on the FFN rank (one kernel)
         x, a_scale = gg.quantize_rows_fp8_cuda(x, ends[-1:], pow2)
     else:
-        a_scale = received.recv_scale
+        a_scale = _fp32_scales(received.recv_scale, x.shape[1])
     if pow2:
         # hardware block scaling end to end: both GEMMs accumulate all of K in tensor memory
         h_q, h_scale = gg.expert_gemm(x, weights.w_gate_up, ends, alignment, swiglu=True, a_scale=a_scale,
@@ -120,7 +130,7 @@ def reference_experts(received: ReceiveResult, weights: ExpertWeights, alignment
     """The same MLP in fp32 torch on the dequantised operands (test oracle)."""
     x, ends = received.recv_x, received.recv_count_psum
     fp8 = weights.mode == "fp8"
-    a_scale = received.recv_scale
+    a_scale = _fp32_scales(received.recv_scale, x.shape[1])
     pow2 = weights.scale_format == "pow2"
     if fp8 and x.dtype != torch.float8_e4m3fn:
         x, a_scale = gg.quantize_rows_fp8(x, pow2)

@@ -96,6 +96,9 @@ def reference_grouped_gemm(a, w, ends, alignment, *, swiglu=False, row_scale=Non
     return out
 
 
+from ..utils.scales import pack_ue8m0x4, unpack_ue8m0x4  # noqa: E402,F401  (re-exported next to the quantisers)
+
+
 def pow2_ceil(scale: torch.Tensor) -> torch.Tensor:
     """Positive fp32 values rounded up to powers of two (exact: mantissa and exponent are split,
     never a logarithm)."""

@@ -13,6 +13,7 @@ import torch.distributed as dist
 
 from ..config import Config
 from ..utils import oracle
+from ..utils.scales import scale_dtype
 
 
 class GlooTransport:
@@ -25,6 +26,7 @@ class GlooTransport:
         self.topk_idx_dtype = torch.int64
         self.payload_dtype = torch.float8_e4m3fn if config.is_fp8 else torch.bfloat16
         self.float32, self.bfloat16 = torch.float32, torch.bfloat16
+        self.scale_dtype = torch.int32 if config.scale_packed else torch.float32      # element type of a row's scales
         self.num_buffer_bytes = 0
         self._launches = 0
         self._slots = None        # attention: per FFN rank, token index of every record
@@ -52,7 +54,7 @@ class GlooTransport:
         c = self.config
         return (
             torch.empty((0, c.hidden_size), dtype=self.payload_dtype),
-            torch.empty((0, c.scale_groups), dtype=torch.float32) if c.is_fp8 else None,
+            torch.empty((0, c.scale_groups), dtype=scale_dtype(c)) if c.is_fp8 else None,
             torch.empty((0, c.top_k), dtype=torch.int64),
             torch.empty((0, c.top_k), dtype=torch.float32),
         )
@@ -61,7 +63,7 @@ class GlooTransport:
         c = self.config
         return (
             torch.empty((0, c.hidden_size), dtype=self.payload_dtype),
-            torch.empty((0, c.scale_groups), dtype=torch.float32) if c.is_fp8 else None,
+            torch.empty((0, c.scale_groups), dtype=scale_dtype(c)) if c.is_fp8 else None,
             torch.empty((0,), dtype=torch.float32),
             torch.zeros((c.experts_per_rank,), dtype=torch.int32),
             torch.empty((0, 2), dtype=torch.int32),
@@ -102,7 +104,7 @@ class GlooTransport:
             sel = torch.where(local[tokens], legal[tokens], torch.full_like(legal[tokens], -1))
             self._send(x[tokens], f)
             if c.is_fp8:
-                self._send(x_scale[tokens].float(), f)
+                self._send(x_scale[tokens].contiguous(), f)
             self._send(sel, f)
             self._send(weights[tokens], f)
             self._send(tokens, f)
@@ -118,7 +120,7 @@ class GlooTransport:
             header = self._recv((1 + el,), torch.int64, src)
             n = int(header[0])
             x = self._recv((n, c.hidden_size), self.payload_dtype, src)
-            scale = self._recv((n, c.scale_groups), torch.float32, src) if c.is_fp8 else None
+            scale = self._recv((n, c.scale_groups), scale_dtype(c), src) if c.is_fp8 else None
             ids = self._recv((n, K), torch.int64, src)
             w = self._recv((n, K), torch.float32, src)
             tokens = self._recv((n,), torch.int64, src)
@@ -127,7 +129,7 @@ class GlooTransport:
         layout = oracle.ffn_layout(torch.stack(headers), c.expert_alignment)
         rows = layout.rows_exact if read_host_counts else c.receive_rows(bucket)
         recv_x = torch.zeros((rows, c.hidden_size), dtype=self.payload_dtype)
-        recv_scale = torch.zeros((rows, c.scale_groups), dtype=torch.float32) if c.is_fp8 else None
+        recv_scale = torch.zeros((rows, c.scale_groups), dtype=scale_dtype(c)) if c.is_fp8 else None
         recv_w = torch.zeros((rows,), dtype=torch.float32)
         recv_src = torch.full((rows, 2), -1, dtype=torch.int32)
         self._records = []

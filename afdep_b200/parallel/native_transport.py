@@ -60,6 +60,7 @@ class NativeTransport:
         self.topk_idx_dtype = torch.int64 if bits == 64 else torch.int32
         self.payload_dtype = torch.float8_e4m3fn if config.is_fp8 else torch.bfloat16
         self.float32, self.bfloat16 = torch.float32, torch.bfloat16
+        self.scale_dtype = torch.int32 if config.scale_packed else torch.float32      # element type of a row's scales
         self._failed: str | None = None
         self._loopback = bool(options.get("loopback", False))
         # recv_scale comes back column-major with a 4-aligned leading dimension, as the reference
@@ -108,6 +109,7 @@ class NativeTransport:
             heap_mode=mode,
             bounds_check=bounds,
             p2p_inflight=int(options.get("p2p_inflight", 4)),
+            scale_packs=config.scale_groups if config.scale_packed else 0,
         )
         self.num_buffer_bytes = int(self._nb.heap_bytes())
         self.num_sms = num_sms
@@ -258,7 +260,7 @@ class NativeTransport:
             dev = torch.device("cuda", self.device)
             self._empty = {
                 "x": torch.empty((0, c.hidden_size), dtype=self.payload_dtype, device=dev),
-                "scale": torch.empty((0, c.scale_groups), dtype=torch.float32, device=dev) if c.is_fp8 else None,
+                "scale": torch.empty((0, c.scale_groups), dtype=self.scale_dtype, device=dev) if c.is_fp8 else None,
                 "ids": torch.empty((0, c.top_k), dtype=torch.int64, device=dev),
                 "w": torch.empty((0, c.top_k), dtype=torch.float32, device=dev),
                 "out": torch.empty((0, c.hidden_size), dtype=torch.bfloat16, device=dev),
@@ -280,6 +282,8 @@ class NativeTransport:
         return self._empties()["out"]
 
     def source_dispatch(self, x, x_scale, ids, weights, *, bucket: int, async_finish: bool = False):
+        if x_scale is not None and self.config.scale_packed:
+            x_scale = x_scale.view(self._torch.float32)      # the kernels move 4-byte elements; the words pass through untouched
         out = self._ranged(
             "source_dispatch",
             lambda: self._on_comm_stream(lambda: self._nb.source_dispatch(x, x_scale, ids, weights), x, x_scale, ids, weights, async_finish=async_finish),
@@ -291,17 +295,22 @@ class NativeTransport:
 
     def worker_receive(self, *, bucket: int, read_host_counts: bool):
         rows = self.config.receive_rows(bucket)
-        return self._ranged(
+        out = self._ranged(
             "worker_receive",
             lambda: self._on_comm_stream(
                 lambda: self._nb.worker_receive(rows, read_host_counts, float(self.config.cpu_timeout_s), self._col_major_scale)
             ),
         )
+        if self.config.scale_packed and out[1] is not None:
+            out = (out[0], out[1].view(self._torch.int32), *out[2:])
+        return out
 
     def worker_mlp_fused(self, weights, *, bucket: int):
         """Layout pass, gathered gate|up GEMM, down GEMM and reply of one exchange; returns
         ``(psum, recv_weights, recv_src, rows)``."""
         fp8 = self.config.is_fp8
+        if self.config.scale_packed:
+            raise ValueError("the fused expert path reads fp32 scales out of the records; with packed scale words use the separate calls")
         if fp8 and (weights.mode != "fp8" or weights.w_down_scale is None or getattr(weights, "scale_format", "fp32") != "pow2"):
             raise ValueError("the fused expert path takes FP8 payloads only with FP8 experts whose block scales are powers of two")
         if not fp8 and weights.mode != "bf16":

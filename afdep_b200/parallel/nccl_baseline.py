@@ -14,6 +14,7 @@ import torch
 import torch.distributed as dist
 
 from ..config import Config
+from ..utils.scales import scale_dtype
 
 
 class NcclBaselineTransport:
@@ -27,6 +28,7 @@ class NcclBaselineTransport:
         self.topk_idx_dtype = torch.int64
         self.payload_dtype = torch.float8_e4m3fn if config.is_fp8 else torch.bfloat16
         self.float32, self.bfloat16 = torch.float32, torch.bfloat16
+        self.scale_dtype = torch.int32 if config.scale_packed else torch.float32      # element type of a row's scales
         self.num_buffer_bytes = 0
         self._launches = 0
         ranks = control.all_gather(dist.get_rank())
@@ -61,7 +63,7 @@ class NcclBaselineTransport:
         c = self.config
         return (
             self._empty((0, c.hidden_size), self.payload_dtype),
-            self._empty((0, c.scale_groups), torch.float32) if c.is_fp8 else None,
+            self._empty((0, c.scale_groups), scale_dtype(c)) if c.is_fp8 else None,
             self._empty((0, c.top_k), torch.int64),
             self._empty((0, c.top_k), torch.float32),
         )
@@ -70,7 +72,7 @@ class NcclBaselineTransport:
         c = self.config
         return (
             self._empty((0, c.hidden_size), self.payload_dtype),
-            self._empty((0, c.scale_groups), torch.float32) if c.is_fp8 else None,
+            self._empty((0, c.scale_groups), scale_dtype(c)) if c.is_fp8 else None,
             self._empty((0,), torch.float32),
             torch.zeros((c.experts_per_rank,), dtype=torch.int32, device=self._dev),
             self._empty((0, 2), torch.int32),
@@ -107,7 +109,7 @@ class NcclBaselineTransport:
         recv_rows = [int(v) for v in got[:, 0].tolist()]                   # host sync
         tok_all = torch.cat(order) if order else torch.empty(0, dtype=torch.int64, device=self._dev)
         payload = self._a2a(x[tok_all], send_rows, recv_rows)
-        scale = self._a2a(x_scale[tok_all].float(), send_rows, recv_rows) if c.is_fp8 else None
+        scale = self._a2a(x_scale[tok_all].contiguous(), send_rows, recv_rows) if c.is_fp8 else None
         rid = self._a2a(ids[tok_all], send_rows, recv_rows)
         rw = self._a2a(weights[tok_all], send_rows, recv_rows)
         rtok = self._a2a(tok_all, send_rows, recv_rows)
@@ -152,7 +154,7 @@ class NcclBaselineTransport:
             recv_x[dst] = payload[r_idx]
         recv_scale = None
         if c.is_fp8:
-            recv_scale = self._empty((rows, c.scale_groups), torch.float32)
+            recv_scale = self._empty((rows, c.scale_groups), scale_dtype(c))
             recv_scale[dst] = scale[r_idx]
         recv_w[dst] = rw[r_idx, k_idx]
         recv_src[dst, 0] = a_idx.to(torch.int32)

@@ -108,7 +108,7 @@ def expected_receive(config: Config, ffn_rank: int, sources: list[SourceBatch], 
         rows = layout.rows_exact
     x0 = sources[0].x
     recv_x = torch.zeros((rows, config.hidden_size), dtype=x0.dtype)
-    recv_scale = torch.zeros((rows, config.scale_groups), dtype=torch.float32) if config.is_fp8 else None
+    recv_scale = torch.zeros((rows, config.scale_groups), dtype=torch.int32 if config.scale_packed else torch.float32) if config.is_fp8 else None
     recv_w = torch.zeros((rows,), dtype=torch.float32)
     recv_src = torch.full((rows, 2), -1, dtype=torch.int32)
     valid = torch.zeros((rows,), dtype=torch.bool)
@@ -136,11 +136,16 @@ def expected_receive(config: Config, ffn_rank: int, sources: list[SourceBatch], 
 
 
 def dequantize(x: torch.Tensor, scale: torch.Tensor | None) -> torch.Tensor:
-    """fp32 view of a payload: e4m3 rows times their per-128 scales, or bf16 rows."""
+    """fp32 view of a payload: e4m3 rows times their per-128 scales (fp32, or int32 words of
+    packed exponent bytes), or bf16 rows."""
     xf = x.float()
     if scale is None:
         return xf
     rows, hidden = xf.shape
+    if scale.dtype == torch.int32:        # exponent bytes packed four to a word
+        from .scales import unpack_ue8m0x4
+
+        scale = unpack_ue8m0x4(scale, hidden // 128)
     return (xf.view(rows, hidden // 128, 128) * scale.float()[:, :, None]).reshape(rows, hidden)
 
 

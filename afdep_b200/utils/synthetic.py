@@ -59,6 +59,15 @@ def quantize_fp8(x: torch.Tensor, pow2: bool = False) -> tuple[torch.Tensor, tor
     return q, scale
 
 
+def _wire_scales(config: Config, scale: torch.Tensor) -> torch.Tensor:
+    """fp32 scales in the form the configuration puts on the wire."""
+    if config.scale_packed:
+        from .scales import pack_ue8m0x4
+
+        return pack_ue8m0x4(scale)
+    return scale
+
+
 def random_batch(config: Config, tokens: int, seed: int, *, zipf_s: float | None = None, skip_fraction: float = 0.0, pow2_scales: bool = False):
     """(x, ids, weights, x_scale) on the CPU for one attention rank."""
     gen = torch.Generator().manual_seed(seed)
@@ -74,8 +83,8 @@ def random_batch(config: Config, tokens: int, seed: int, *, zipf_s: float | None
         ids = torch.where(drop, torch.full_like(ids, -1), ids)
         weights = torch.where(drop, torch.zeros_like(weights), weights)
     if config.is_fp8:
-        q, scale = quantize_fp8(x, pow2_scales)
-        return q, ids, weights, scale
+        q, scale = quantize_fp8(x, pow2_scales or config.scale_packed)
+        return q, ids, weights, _wire_scales(config, scale)
     return x.to(torch.bfloat16), ids, weights, None
 
 
@@ -103,8 +112,8 @@ def exact_batch(config: Config, tokens: int, source: int, epoch: int, *, active:
     ids = torch.where(live[:, None], ids, torch.full_like(ids, -1))
     weights = torch.where(live[:, None] & (ids >= 0), weights, torch.zeros_like(weights))
     if config.is_fp8:
-        groups = torch.arange(config.scale_groups)
+        groups = torch.arange(H // 128)
         scale = (2.0 ** (groups % 3 - 1).float())[None, :].expand(tokens, -1).contiguous()
         q = (x.view(tokens, -1, 128) / scale[:, :, None]).reshape(tokens, H).to(torch.float8_e4m3fn)
-        return q, ids, weights, scale
+        return q, ids, weights, _wire_scales(config, scale)
     return x.to(torch.bfloat16), ids, weights, None

@@ -64,3 +64,14 @@ def test_known_geometry_of_the_headline_config():
     g = load_native().geometry(2, 2, 4096, 8, 128, 2048, False, 128, 0)
     assert (g["rec_bytes"], g["row_bytes"], g["experts_local"]) == (8320, 8192, 64)      # 8 KB row + 100 B of routing words, padded
     assert g["f_bytes"] < 68 << 20                                                        # registered bytes per FFN rank
+
+
+def test_packed_scale_words_shrink_the_record():
+    """56 fp32 scales take 224 bytes of a 7168-wide FP8 record; as 14 words of four exponent bytes
+    they take 64 (padded to 16), and everything behind them moves up."""
+    lib = load_native()
+    fp32 = lib.geometry(2, 2, 7168, 8, 128, 256, True, 128, 0)
+    packed = lib.geometry(2, 2, 7168, 8, 128, 256, True, 128, 0, scale_packs=14)
+    assert (fp32["scale_bytes"], packed["scale_bytes"]) == (224, 64)
+    assert packed["meta_off"] == 7168 + 64 and packed["meta_off"] % 16 == 0
+    assert packed["rec_bytes"] % 128 == 0 and packed["rec_bytes"] <= fp32["rec_bytes"]

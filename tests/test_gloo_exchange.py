@@ -18,13 +18,19 @@ from tests._dist import run_ranks
 def _exchange(rank, world, payload, read_host_counts):
     import torch.distributed as dist
 
-    cfg = Config(16, 256, 8, 2, 2, 2, expert_alignment=4, payload=payload)
+    packed = payload == "fp8-packed"          # FP8 rows whose scales travel as packed exponent bytes
+    cfg = Config(16, 256, 8, 2, 2, 2, expert_alignment=4, payload="fp8" if packed else payload,
+                 scale_format="ue8m0x4" if packed else "fp32")
     buf = Buffer(group=dist.group.WORLD, config=cfg, backend="gloo")
     assert buf.role == ("ffn" if rank < 2 else "attention")
     for epoch in range(3):
         batches = [synthetic.exact_batch(cfg, 16, a, epoch, active=16 - 5 * a * (epoch % 2)) for a in range(2)]
         if buf.role == "attention":
             x, ids, w, scale = batches[buf.role_rank]
+            if packed:
+                assert scale.dtype == torch.int32 and scale.shape == (x.shape[0], 1)
+                with pytest.raises(ValueError, match="dtype, shape"):
+                    buf.source_dispatch(x, ids, w, oracle.dequantize(torch.ones_like(x), scale)[:, :2].contiguous(), bucket=16)
             buf.source_dispatch(x, ids, w, scale, bucket=16, read_host_counts=read_host_counts)
             with pytest.raises(RuntimeError, match="previous exchange"):
                 buf.source_dispatch(x, ids, w, scale, bucket=16)
@@ -39,6 +45,9 @@ def _exchange(rank, world, payload, read_host_counts):
             assert torch.equal(rec.recv_count_psum.long(), exp.layout.ends)
             v = exp.valid
             assert torch.equal(rec.recv_x[v].float(), exp.recv_x[v].float())
+            if cfg.is_fp8:
+                assert rec.recv_scale.dtype == (torch.int32 if packed else torch.float32)
+                assert torch.equal(rec.recv_scale[v], exp.recv_scale[v])
             assert torch.equal(rec.recv_topk_weights[v], exp.recv_weights[v])
             assert torch.equal(rec.handle.recv_src_metadata[v], exp.recv_src[v])
             if read_host_counts:
@@ -54,7 +63,7 @@ def _exchange(rank, world, payload, read_host_counts):
     buf.close()   # idempotent
 
 
-@pytest.mark.parametrize("payload", ["bf16", "fp8"])
+@pytest.mark.parametrize("payload", ["bf16", "fp8", "fp8-packed"])
 @pytest.mark.parametrize("read_host_counts", [False, True])
 def test_four_rank_exchange(payload, read_host_counts):
     run_ranks(_exchange, 4, payload, read_host_counts)

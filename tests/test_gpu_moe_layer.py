@@ -118,3 +118,31 @@ def test_moe_layer_matches_dense_reference(payload, mode, down, scale_format, fu
             torch.testing.assert_close(out.float(), want, rtol=5e-2, atol=5e-3 if weights[0].w_down_scale is None else 1.2e-2)
     finally:
         world.close()
+
+
+def test_packed_scales_feed_the_experts_like_fp32_scales():
+    """The same FP8 rows dispatched with fp32 power-of-two scales and with the scales packed as
+    exponent bytes give bit-identical layer outputs (the FFN rank expands the words)."""
+    from afdep_b200.parallel.loopback import LoopbackWorld
+
+    hidden, inter, experts, top_k, ffn, attn, tokens = 512, 256, 8, 2, 2, 2, 80
+    outs = {}
+    for fmt in ("fp32", "ue8m0x4"):
+        cfg = Config(tokens, hidden, experts, top_k, ffn, attn, expert_alignment=128, payload="fp8", scale_format=fmt)
+        world = LoopbackWorld(cfg, gpu_timeout_s=5.0)
+        try:
+            weights = [ExpertWeights.random(cfg.experts_per_rank, hidden, inter, mode="fp8", down="fp8", seed=10 + f, scale_format="pow2")
+                       for f in range(ffn)]
+            batches = [synthetic.random_batch(cfg, tokens - 7 * a, seed=a, pow2_scales=True) for a in range(attn)]
+            assert all(b[3].dtype == (torch.int32 if fmt == "ue8m0x4" else torch.float32) for b in batches)
+            dev = [tuple(None if t is None else t.cuda() for t in b) for b in batches]
+            out, _ = world.exchange(dev, lambda i, rec: run_experts(rec, weights[i], cfg.expert_alignment))
+            torch.cuda.synchronize()
+            for b in world.buffers:
+                b.check()
+            outs[fmt] = [o.clone() for o in out]
+        finally:
+            world.close()
+    assert not gg.gemm_check()
+    for a, b in zip(outs["fp32"], outs["ue8m0x4"]):
+        assert torch.equal(a, b) and bool(a.float().abs().sum() > 0)

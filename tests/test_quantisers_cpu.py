@@ -1,6 +1,7 @@
 """CPU checks of the plain-torch quantisers the GPU kernels are tested against, and of the small
 host-side pieces added beside them (power-of-two scale rounding, the event hand-back object)."""
 
+import pytest
 import torch
 
 from afdep_b200.ops import grouped_gemm as gg
@@ -59,3 +60,35 @@ def test_event_handle_without_a_stream_is_a_no_op():
     h.current_stream_wait()
     h.synchronize()
     assert h._keep_alive == ()
+
+
+def test_ue8m0x4_pack_round_trip_and_refusals():
+    """Exponent bytes four to an int32 word: every fp32 power of two survives, padding bytes carry
+    the exponent of 1.0, strided inputs are read as they are, anything else is refused."""
+    from afdep_b200.utils.scales import UE8M0_ONE, pack_ue8m0x4, unpack_ue8m0x4
+
+    g = torch.Generator().manual_seed(5)
+    scale = torch.ldexp(torch.ones(9, 7), torch.randint(-126, 128, (9, 7), generator=g))
+    scale[0, 3], scale[1, 0] = 2.0 ** 127, 2.0 ** -126        # both ends of the range; the first sets a word's sign bit
+    words = pack_ue8m0x4(scale)
+    assert words.dtype == torch.int32 and words.shape == (9, 2)
+    assert torch.equal(unpack_ue8m0x4(words, 7), scale)
+    assert torch.equal((words[:, 1].long() >> 24) & 0xFF, torch.full((9,), UE8M0_ONE))      # the eighth byte is padding
+    col_major = words.t().contiguous().t()
+    assert not col_major.is_contiguous() and torch.equal(unpack_ue8m0x4(col_major, 7), scale)
+    for bad in (torch.tensor([[3.0]]), torch.tensor([[0.0]]), torch.tensor([[-2.0]]), torch.tensor([[1e-40]])):
+        with pytest.raises(ValueError, match="power-of-two"):
+            pack_ue8m0x4(bad)
+
+
+def test_config_scale_format():
+    from afdep_b200 import Config
+
+    c = Config(16, 7168, 8, 2, 2, 2, payload="fp8", scale_format="ue8m0x4")
+    assert c.scale_packed and c.scale_groups == 14                 # 56 scales, four to a word
+    assert Config(16, 768, 8, 2, 2, 2, payload="fp8", scale_format="ue8m0x4").scale_groups == 2     # 6 scales: padded
+    assert Config(16, 7168, 8, 2, 2, 2, payload="fp8").scale_groups == 56
+    with pytest.raises(ValueError, match="scale_format"):
+        Config(16, 512, 8, 2, 2, 2, payload="fp8", scale_format="e8m0")
+    with pytest.raises(ValueError, match="FP8 payloads only"):
+        Config(16, 512, 8, 2, 2, 2, scale_format="ue8m0x4")
