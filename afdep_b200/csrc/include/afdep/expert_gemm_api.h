@@ -43,9 +43,14 @@ struct ExpertGemmArgs {
 
     // Scales (mx only).  Dense: element (row, kb) at a_scale[row * s0 + kb * s1].  Gathered: K/128
     // floats at byte offset a_scale_off inside the gathered row's record.
+    // With a_scale_packed the scales are exponent bytes (UE8M0) packed four to a 32-bit word, one word
+    // per row and group of four K blocks: a_scale then points at words ([rows, ceil(K / 512)], strides
+    // in words), and a gathered record holds ceil(K / 512) words at a_scale_off.  The words go to
+    // tensor memory as they are.
     const float* a_scale;
     long long a_scale_s0, a_scale_s1;
     int a_scale_off;
+    int a_scale_packed;
     const float* w_scale;    // [experts][N / 128][K / 128]
 
     // Epilogue.

@@ -413,6 +413,8 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             // Scales of one group (four K blocks): four rows per lane for A, two 128-column blocks for W.
             // They are fetched one group ahead, so their latency never holds up the row gathering.
             float sa[4][4], sb[2][4];
+            uint32_t pa[4];                              // packed form: one word per row holds the group's four exponent bytes
+            const bool a_packed = kMx && p.a_scale_packed != 0;
             const int kgroups = p.K / 128;
             const bool from_records = kGather && p.a_scale == nullptr;
             const float4* rec_scale[4];                  // gathered rows: the scales sit in the record, behind the payload
@@ -429,7 +431,16 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int r = 32 * j + lane;
-                    if (from_records) {
+                    if (a_packed) {
+                        uint32_t word = 0x7f7f7f7fu;             // four times the exponent of 1.0
+                        if (from_records) {
+                            if (rec_scale[j] != nullptr) word = __ldcg(reinterpret_cast<const uint32_t*>(rec_scale[j]) + (kb0 >> 2));
+                        } else if (row0 + r < row_limit) {
+                            word = __ldg(reinterpret_cast<const uint32_t*>(p.a_scale) + (size_t)(row0 + r) * p.a_scale_s0 +
+                                         (size_t)(kb0 >> 2) * p.a_scale_s1);
+                        }
+                        pa[j] = word;
+                    } else if (from_records) {
                         float4 v = make_float4(1.f, 1.f, 1.f, 1.f);
                         if (rec_scale[j] != nullptr) v = __ldcg(rec_scale[j] + (kb0 >> 2));
                         sa[j][0] = v.x;
@@ -471,6 +482,11 @@ expert_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             uint32_t wa[4], wb[2];
             auto pack_rows = [&](int kb0) {
                 const bool whole = kb0 + 4 <= num_kb;
+                if (a_packed) {                          // bytes past the last K block are never read by an MMA
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) wa[j] = pa[j];
+                    return;
+                }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     uint32_t word = 0;

@@ -362,8 +362,6 @@ public:
                                const torch::Tensor& w_down, const c10::optional<torch::Tensor>& w_down_scale, int64_t rows_bound) {
         live();
         TORCH_CHECK(is_ffn_, "worker_mlp_fused runs on FFN ranks");
-        TORCH_CHECK(!geo_.fp8 || geo_.scale_groups == geo_.hidden / 128,
-                    "the fused expert path reads fp32 scales out of the records; packed scale words take the separate calls");
         const int EL = geo_.experts_local, H = geo_.hidden;
         const bool fp8 = geo_.fp8 != 0;
         const auto wdt = fp8 ? torch::kFloat8_e4m3fn : torch::kBFloat16;
@@ -418,6 +416,7 @@ public:
         g.a_pitch = geo_.rec_bytes;
         g.row_rec = row_rec.data_ptr<int>();
         g.a_scale_off = fp8 ? geo_.payload_bytes : -1;
+        g.a_scale_packed = (fp8 && geo_.scale_groups != geo_.hidden / 128) ? 1 : 0;      // the Buffer carries packed exponent words
         g.w_scale = fp8 ? w_gate_up_scale->data_ptr<float>() : nullptr;
         g.swiglu = 1;
         g.ldc = (int)I;
@@ -840,7 +839,7 @@ py::object grouped_gemm(const torch::Tensor& a, const torch::Tensor& w, const to
 py::object expert_gemm(const torch::Tensor& a, const torch::Tensor& w, const torch::Tensor& ends, int64_t alignment, bool swiglu,
                        const c10::optional<torch::Tensor>& row_scale, const c10::optional<torch::Tensor>& a_scale,
                        const c10::optional<torch::Tensor>& w_scale, const c10::optional<torch::Tensor>& out_opt, int64_t ctas,
-                       bool quantize_out, const c10::optional<torch::Tensor>& row_index, int64_t a_scale_offset) {
+                       bool quantize_out, const c10::optional<torch::Tensor>& row_index, int64_t a_scale_offset, bool a_scale_packed) {
     TORCH_CHECK(a.is_cuda() && w.is_cuda() && ends.is_cuda(), "expert_gemm needs CUDA tensors");
     TORCH_CHECK(a.dim() == 2 && w.dim() == 3 && a.is_contiguous() && w.is_contiguous(), "a 2-D, w [experts,N,K], contiguous");
     const bool fp8 = w.scalar_type() == torch::kFloat8_e4m3fn;
@@ -894,15 +893,26 @@ py::object expert_gemm(const torch::Tensor& a, const torch::Tensor& w, const tor
         TORCH_CHECK(w_scale.has_value() && w_scale->scalar_type() == torch::kFloat32 && w_scale->is_contiguous() &&
                         w_scale->numel() == E * (N / 128) * (K / 128), "w_scale: fp32 [experts, N/128, K/128]");
         g.w_scale = w_scale->data_ptr<float>();
-        if (a_scale.has_value()) {
+        const int64_t words = (K / 128 + 3) / 4;        // packed form: four exponent bytes to a word
+        if (a_scale.has_value() && a_scale->scalar_type() == torch::kInt32) {
+            TORCH_CHECK(a_scale->is_cuda() && a_scale->dim() == 2 && a_scale->size(0) == rows && a_scale->size(1) == words,
+                        "packed a_scale: int32 [rows, ceil(K/512)]");
+            g.a_scale = reinterpret_cast<const float*>(a_scale->data_ptr<int>());
+            g.a_scale_s0 = a_scale->stride(0);
+            g.a_scale_s1 = a_scale->stride(1);
+            g.a_scale_packed = 1;
+        } else if (a_scale.has_value()) {
             TORCH_CHECK(a_scale->scalar_type() == torch::kFloat32 && a_scale->size(0) == rows && a_scale->size(1) == K / 128, "a_scale: fp32 [rows, K/128]");
             g.a_scale = a_scale->data_ptr<float>();
             g.a_scale_s0 = a_scale->stride(0);
             g.a_scale_s1 = a_scale->stride(1);
         } else {
-            TORCH_CHECK(gather && a_scale_offset >= K && a_scale_offset % 16 == 0 && a_scale_offset + ((K / 128 + 3) / 4) * 16 <= g.a_pitch,
-                        "FP8 operands need a_scale, or gathered records with the scales (padded to whole 16-byte groups) at a 16-byte aligned a_scale_offset");
+            TORCH_CHECK(gather && a_scale_offset >= K && a_scale_offset % 16 == 0 &&
+                            a_scale_offset + (a_scale_packed ? words * 4 : words * 16) <= g.a_pitch,
+                        "FP8 operands need a_scale, or gathered records with the scales (fp32 padded to whole 16-byte groups, or packed words) "
+                        "at a 16-byte aligned a_scale_offset");
             g.a_scale_off = (int)a_scale_offset;
+            g.a_scale_packed = a_scale_packed ? 1 : 0;
         }
     }
     g.out = quantize_out ? nullptr : reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
@@ -1017,7 +1027,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("w_scale") = py::none(), py::arg("out") = py::none(), py::arg("ctas") = 0, py::arg("quantize_out") = false);
     m.def("expert_gemm", &afdep::expert_gemm, py::arg("a"), py::arg("w"), py::arg("ends"), py::arg("alignment"), py::arg("swiglu") = false,
           py::arg("row_scale") = py::none(), py::arg("a_scale") = py::none(), py::arg("w_scale") = py::none(), py::arg("out") = py::none(),
-          py::arg("ctas") = 0, py::arg("quantize_out") = false, py::arg("row_index") = py::none(), py::arg("a_scale_offset") = -1);
+          py::arg("ctas") = 0, py::arg("quantize_out") = false, py::arg("row_index") = py::none(), py::arg("a_scale_offset") = -1,
+          py::arg("a_scale_packed") = false);
     // True (and cleared) if an expert GEMM on this device gave up on a bounded wait since the last check.
     m.def("gemm_check", [](int device) {
         const afdep::GemmErrorWord w = afdep::gemm_error_word(device);

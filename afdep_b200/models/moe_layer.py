@@ -109,7 +109,8 @@ def run_experts(received: ReceiveResult, weights: ExpertWeights, alignment: int,
         # BF16 dispatch into FP8 experts: quantise the live rows on the FFN rank (one kernel)
         x, a_scale = gg.quantize_rows_fp8_cuda(x, ends[-1:], pow2)
     else:
-        a_scale = _fp32_scales(received.recv_scale, x.shape[1])
+        # packed exponent words go to the block-scaled kernel as they are; the promoting kernel wants fp32
+        a_scale = received.recv_scale if pow2 else _fp32_scales(received.recv_scale, x.shape[1])
     if pow2:
         # hardware block scaling end to end: both GEMMs accumulate all of K in tensor memory
         h_q, h_scale = gg.expert_gemm(x, weights.w_gate_up, ends, alignment, swiglu=True, a_scale=a_scale,

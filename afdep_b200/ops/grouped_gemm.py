@@ -34,7 +34,7 @@ def grouped_gemm(a, w, ends, alignment: int, *, swiglu: bool = False, row_scale=
 
 
 def expert_gemm(a, w, ends, alignment: int, *, swiglu: bool = False, row_scale=None, a_scale=None, w_scale=None, out=None, ctas: int = 0,
-                quantize_out: bool = False, row_index=None, a_scale_offset: int = -1):
+                quantize_out: bool = False, row_index=None, a_scale_offset: int = -1, a_scale_packed: bool = False):
     """The self-feeding kernel: BF16, or e4m3 whose fp32 block scales are **powers of two**
     (``quantize_*(..., pow2=True)``).  The tensor core applies the scales itself
     (``tcgen05.mma ... block_scale``), so the whole K extent accumulates in tensor memory.
@@ -43,11 +43,15 @@ def expert_gemm(a, w, ends, alignment: int, *, swiglu: bool = False, row_scale=N
     space is read from ``a[row_index[r]]`` (negative: a row of zeros), ``a`` being any contiguous
     2-D tensor whose rows start with the K operand elements -- for instance the wire records of an
     exchange, viewed as ``uint8 [records, record_bytes]`` with each record's fp32 scales at byte
-    offset ``a_scale_offset``.  ``quantize_out`` returns e4m3 with power-of-two scales."""
+    offset ``a_scale_offset``.  ``quantize_out`` returns e4m3 with power-of-two scales.
+
+    The scales of ``a`` may also come as exponent bytes packed four to an int32 word
+    (``utils.scales.pack_ue8m0x4``): pass ``a_scale`` as int32 ``[rows, ceil(K/512)]`` (any strides), or
+    ``a_scale_packed=True`` for words inside gathered records; they reach tensor memory unconverted."""
     from .._native import load_native
 
     return load_native().expert_gemm(a, w, ends, int(alignment), bool(swiglu), row_scale, a_scale, w_scale, out, int(ctas), bool(quantize_out),
-                                     row_index, int(a_scale_offset))
+                                     row_index, int(a_scale_offset), bool(a_scale_packed))
 
 
 def gemm_check(device: int | None = None) -> bool:

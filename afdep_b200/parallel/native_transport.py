@@ -309,8 +309,6 @@ class NativeTransport:
         """Layout pass, gathered gate|up GEMM, down GEMM and reply of one exchange; returns
         ``(psum, recv_weights, recv_src, rows)``."""
         fp8 = self.config.is_fp8
-        if self.config.scale_packed:
-            raise ValueError("the fused expert path reads fp32 scales out of the records; with packed scale words use the separate calls")
         if fp8 and (weights.mode != "fp8" or weights.w_down_scale is None or getattr(weights, "scale_format", "fp32") != "pow2"):
             raise ValueError("the fused expert path takes FP8 payloads only with FP8 experts whose block scales are powers of two")
         if not fp8 and weights.mode != "bf16":

@@ -214,9 +214,22 @@ def test_gathered_rows_match_the_dense_product(dtype):
         got = gg.expert_gemm(records, w, ends.cuda(), 128, w_scale=w_scale, row_index=index.cuda(), a_scale_offset=K)
         want = gg.expert_gemm(dense, w, ends.cuda(), 128, a_scale=dense_scale, w_scale=w_scale)
         ref = gg.reference_grouped_gemm(dense, w, ends, 128, a_scale=dense_scale, w_scale=w_scale)
+        # the same scales as exponent bytes packed four to a word: dense (row- and column-major words)
+        # and inside the records
+        words = gg.pack_ue8m0x4(dense_scale)
+        packed = [gg.expert_gemm(dense, w, ends.cuda(), 128, a_scale=words, w_scale=w_scale),
+                  gg.expert_gemm(dense, w, ends.cuda(), 128, a_scale=words.t().contiguous().t(), w_scale=w_scale)]
+        rec_words = gg.pack_ue8m0x4(sc)
+        records2 = torch.zeros(n_rec, K + 128, dtype=torch.uint8, device="cuda")
+        records2[:, :K] = q.view(torch.uint8)
+        records2[:, K : K + rec_words.shape[1] * 4] = rec_words.contiguous().view(torch.uint8).view(n_rec, -1)
+        packed.append(gg.expert_gemm(records2, w, ends.cuda(), 128, w_scale=w_scale, row_index=index.cuda(), a_scale_offset=K, a_scale_packed=True))
     torch.cuda.synchronize()
     starts = gg.segment_starts(ends, 128).tolist()
     for s0, t0 in zip(starts, ends.tolist()):
         assert torch.equal(got[s0:t0], want[s0:t0])
+        if dtype == "fp8":
+            for other in packed:
+                assert torch.equal(other[s0:t0], want[s0:t0])
         torch.testing.assert_close(got[s0:t0].float(), ref[s0:t0], rtol=2e-2, atol=2e-2)
     assert not gg.gemm_check()

@@ -449,8 +449,7 @@ def test_expert_stats_accumulate_on_the_device():
 @pytest.mark.parametrize("hidden,ffn,attn", [(1024, 2, 2), (768, 1, 3), (7168, 2, 2)])
 def test_scales_as_packed_exponent_bytes(hidden, ffn, attn):
     """``scale_format="ue8m0x4"``: the FP8 rows' scales travel as int32 words of four exponent bytes
-    (6 scales pad to 2 words at hidden 768) and come back bit for bit, in the column-major layout too;
-    the fused expert path, which reads fp32 scales out of the records, refuses such a Buffer."""
+    (6 scales pad to 2 words at hidden 768) and come back bit for bit, in the column-major layout too."""
     cfg = Config(64, hidden, 16, 4, ffn, attn, expert_alignment=8, payload="fp8", scale_format="ue8m0x4")
     assert cfg.scale_groups == (hidden // 128 + 3) // 4
     world = make_world(cfg)
@@ -465,7 +464,5 @@ def test_scales_as_packed_exponent_bytes(hidden, ffn, attn):
         x, ids, w, scale = to_dev(batches[0])
         with pytest.raises(ValueError, match="dtype, shape"):
             world.attention[0].source_dispatch(x, ids, w, torch.ones((x.shape[0], hidden // 128), device="cuda"), bucket=64)
-        with pytest.raises(ValueError, match="separate calls"):
-            world.ffn[0]._t.worker_mlp_fused(None, bucket=64)
     finally:
         world.close()

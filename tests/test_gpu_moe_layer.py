@@ -122,7 +122,8 @@ def test_moe_layer_matches_dense_reference(payload, mode, down, scale_format, fu
 
 def test_packed_scales_feed_the_experts_like_fp32_scales():
     """The same FP8 rows dispatched with fp32 power-of-two scales and with the scales packed as
-    exponent bytes give bit-identical layer outputs (the FFN rank expands the words)."""
+    exponent bytes give bit-identical layer outputs, through the separate calls (the words go to
+    the block-scaled GEMM as they are) and through the fused path (which reads them out of the records)."""
     from afdep_b200.parallel.loopback import LoopbackWorld
 
     hidden, inter, experts, top_k, ffn, attn, tokens = 512, 256, 8, 2, 2, 2, 80
@@ -141,8 +142,18 @@ def test_packed_scales_feed_the_experts_like_fp32_scales():
             for b in world.buffers:
                 b.check()
             outs[fmt] = [o.clone() for o in out]
+            for buf, (x, ids, w, scale) in zip(world.attention, dev):
+                buf.source_dispatch(x, ids, w, scale, bucket=tokens)
+            for i, buf in enumerate(world.ffn):
+                buf.worker_serve_fused(weights[i], bucket=tokens)
+            outs[fmt + "/fused"] = [buf.source_collect().clone() for buf in world.attention]
+            torch.cuda.synchronize()
+            for b in world.buffers:
+                b.check()
         finally:
             world.close()
     assert not gg.gemm_check()
-    for a, b in zip(outs["fp32"], outs["ue8m0x4"]):
-        assert torch.equal(a, b) and bool(a.float().abs().sum() > 0)
+    for k, a in enumerate(outs["fp32"]):
+        assert bool(a.float().abs().sum() > 0)
+        for other in ("ue8m0x4", "fp32/fused", "ue8m0x4/fused"):
+            assert torch.equal(a, outs[other][k]), other
