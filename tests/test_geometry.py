@@ -2,7 +2,6 @@
 the alignment rules the bulk copies depend on (16-byte addresses and sizes), that the regions of a
 heap do not overlap and are large enough, and that every launch fits an SM's shared memory."""
 
-import pytest
 from hypothesis import given, settings
 from hypothesis import strategies as st
 
