@@ -66,6 +66,8 @@ def parse_args():
     p.add_argument("--expert-down", choices=("fp8", "bf16"), default=None, help="config 5: storage of the down projection (default: like --expert-weights)")
     p.add_argument("--expert-scales", choices=("pow2", "fp32"), default="pow2",
                    help="config 5, FP8: block scales rounded up to powers of two and applied by the tensor core (default), or arbitrary fp32 scales promoted through registers")
+    p.add_argument("--scale-format", choices=("fp32", "ue8m0x4"), default="fp32",
+                   help="FP8 payloads: scales on the wire as fp32 (the reference's contract) or as packed exponent bytes")
     p.add_argument("--unfused", action="store_true", help="config 5: worker_receive -> experts -> worker_reply as separate calls")
     p.add_argument("--no-extra", action="store_true", help="--gpus 8: skip the sub-results for configs 3, 4 and 5")
     p.add_argument("--max-rounds", type=int, default=400, help="upper bound on the rounds of K steps (1 for a profiler capture)")
@@ -253,8 +255,9 @@ def run_config(env: Env, name: str, *, steps: int, warmup: int, tokens: int = 0,
     payload = spec["payload"]
     if experts_on and args.expert_weights == "bf16":
         payload = "bf16"
+    packed = args.scale_format == "ue8m0x4" and payload == "fp8"
     cfg = Config(T, spec["hidden"], spec["experts_per_ffn"] * ffn, spec["top_k"], ffn, attn, payload=payload, num_sms=args.num_sms,
-                 gpu_timeout_s=20, cpu_timeout_s=60)
+                 gpu_timeout_s=20, cpu_timeout_s=60, scale_format="ue8m0x4" if packed else "fp32")
     world_obj = None
     if multi:
         import torch.distributed as dist
@@ -618,6 +621,7 @@ def run_config(env: Env, name: str, *, steps: int, warmup: int, tokens: int = 0,
             "top_k": cfg.top_k,
             "tokens_per_attention_rank": T,
             "payload": cfg.payload,
+            **({"scales_on_wire": cfg.scale_format} if cfg.is_fp8 else {}),
             "routing": "zipf(1.1)" if spec["zipf"] else "uniform",
             "l2": "flushed between steps (256 MiB fill); e2e: inputs arrive from host memory every step",
             "mode": "cuda-graph replay of complete exchanges" if use_graph else "eager",
