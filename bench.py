@@ -22,7 +22,7 @@ entry repeats the measurement with, inside the timed region and every step, the 
 copy of the step's inputs from pinned memory (one block per rank, one copy) and a device->host read of a checksum of the
 result: ``serial`` issues the copy on the compute stream, the headline e2e ``value`` stages
 step n+1's copy on a second stream while step n runs.  With ``--gpus 8`` the line also carries
-sub-results for the 8-GPU configurations 3, 4 and 5 under ``extra``.
+sub-results for the 8-GPU configurations 3, 4 and 5 (5 both fused and as separate calls) under ``extra``.
 """
 
 from __future__ import annotations
@@ -684,10 +684,19 @@ def main() -> None:
     if env.n == 8 and args.config == "weak" and args.impl == "ours" and not args.no_extra:
         # the 8-GPU configurations, measured in the same run: skewed FP8 prefill, decode, end-to-end MoE layer
         extra = {}
+        keys = ("value", "us_per_exchange", "us_per_exchange_p10", "us_per_exchange_p90", "per_rank_GBs", "rounds",
+                "steps", "dtype", "config", "phases", "roofline", "expert_tflops", "experts", "gpu_launches")
         for name, k in (("3", 20), ("4", 100), ("5", 10)):
             sub = run_config(env, name, steps=k, warmup=3, with_e2e=False)
-            extra["config" + name] = {key: sub[key] for key in ("value", "us_per_exchange", "us_per_exchange_p10", "us_per_exchange_p90", "per_rank_GBs", "rounds",
-                                                              "steps", "dtype", "config", "phases", "roofline", "expert_tflops", "experts", "gpu_launches")}
+            extra["config" + name] = {key: sub[key] for key in keys}
+        if not args.unfused:
+            # the same MoE step with worker_receive -> experts -> worker_reply as separate calls, next to the fused one
+            args.unfused = True
+            try:
+                sub = run_config(env, "5", steps=10, warmup=3, with_e2e=False)
+            finally:
+                args.unfused = False
+            extra["config5_separate_calls"] = {key: sub[key] for key in keys}
         result["extra"] = extra
     # the sampler runs through every pass of this invocation: all of it is under load
     clocks = sampler.stop() if env.rank == 0 else None
